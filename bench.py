@@ -1,0 +1,403 @@
+#!/usr/bin/env python3
+"""Benchmark of the W4A16 hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-prefill] [--no-cpu]
+
+Headline (`value`): the OPT-6.7B-shaped decode sweep - M in {1,4,8,16} on (K,N) in
+{(4096,4096), (4096,16384), (16384,4096)}, g=128 - as achieved HBM GB/s (algorithmic bytes /
+device time), inputs resident in HBM.  One step = the 12 (shape, M) launches, each run once on
+every one of SETS distinct weight sets (rotating, so the bytes touched between two uses of a set
+exceed the 126 MB L2).  The step is captured in a CUDA graph; K graph replays are timed with CUDA
+events on the launching stream.  Extra keys: `e2e` (same sweep through the host-buffer C-ABI call),
+`roofline`, `cpu_baseline`, `prefill` (tcgen05 GEMM TFLOP/s, M in {512,2048,8192}), `sweep`
+(per-shape decode numbers), `clocks`.
+
+`--impl reference` times the CPU restatement of the reference path (dequantise + fp32 matmul) on
+the host cores instead; the reference ships no CPU implementation of its own.
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "sparse-quant_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+METRIC = "w4a16_decode_gemv_hbm_gbs"
+UNIT = "GB/s"
+G = 128
+DECODE_SHAPES = [(4096, 4096), (4096, 16384), (16384, 4096)]     # (K, N)
+DECODE_M = [1, 4, 8, 16]
+PREFILL_M = [512, 2048, 8192]
+SETS = 4                                                         # distinct weight sets per shape
+WORKLOAD = "OPT-6.7B decode GEMV sweep: M in {1,4,8,16} x (K,N) in {4096x4096, 4096x16384, 16384x4096}, g=128"
+
+
+def decode_bytes(M, K, N, g=G, bias=False):
+    """Algorithmic bytes of one call: packed weights + (zero, scale) pairs + x + y (+ bias)."""
+    return K * N // 2 + (K // g) * N * 4 + M * K * 2 + M * N * 2 + (2 * N if bias else 0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic packed weights (random nibbles / scales with the value distribution of a quantised
+# N(0, 0.02) weight: zero points around 7-8, scales ~ 6 sigma / 15), generated on the device
+# ---------------------------------------------------------------------------------------------
+def synth_packed(K, N, g, device, seed):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device=device, generator=gen)
+    zeros = torch.randint(5, 11, (K // g, N), device=device, generator=gen).to(torch.float16) + 64.0
+    scales = (torch.rand((K // g, N), device=device, generator=gen) * 0.004 + 0.006).to(torch.float16)
+    zs = torch.stack([zeros, scales], dim=-1).reshape(K // g, 2 * N).contiguous()
+    return qw, zs
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples = []
+        self.stop = False
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.ok:
+            self.t.start()
+
+    def finish(self, t0, t1):
+        self.stop = True
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self.t.join(timeout=1.0)
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        use = inside or self.samples[-3:]
+        names = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        bits = 0
+        for s in use:
+            bits |= s[2]
+        bits &= ~0x1 if inside else bits
+        reasons = [n for b, n in names.items() if bits & b]
+        mhz = sorted(s[1] for s in use)
+        return {"sm_mhz": (mhz[len(mhz) // 2] if mhz else None), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples_in_region": len(inside)}
+
+
+# ---------------------------------------------------------------------------------------------
+# reference / CPU arm
+# ---------------------------------------------------------------------------------------------
+def cpu_pass(K, N, M, qw_np, zs_np, x):
+    import oracle
+    w = oracle.dequant_f32(qw_np, zs_np, K, N, G)                 # C + OpenMP, bit-exact dequantisation
+    return torch.matmul(x.float(), torch.from_numpy(w).t())       # fp32 matmul on all host threads
+
+
+def cpu_baseline(repeat=1, budget_s=25.0):
+    import oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    K, N, M = 4096, 4096, 16
+    rng = np.random.default_rng(0)
+    qw = rng.integers(0, 2 ** 32, size=(K, N // 8), dtype=np.uint32)
+    zs = np.empty((K // G, 2 * N), dtype=np.float16)
+    zs[:, 0::2] = rng.integers(5, 11, size=(K // G, N)) + 64
+    zs[:, 1::2] = rng.random((K // G, N)) * 0.004 + 0.006
+    x = torch.randn(M, K).half()
+    cpu_pass(K, N, M, qw, zs.view(np.uint16), x)                  # warm
+    t0 = time.perf_counter()
+    n = 0
+    while n < repeat and (n == 0 or time.perf_counter() - t0 < budget_s):
+        cpu_pass(K, N, M, qw, zs.view(np.uint16), x)
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    return dict(value=decode_bytes(M, K, N) / dt / 1e9, unit=UNIT, cores=max(oracle.num_threads(), torch.get_num_threads()),
+                kind="port", sample=f"{n} pass(es) of the K=4096 N=4096 M=16 call (dequantise in C/OpenMP + torch fp32 matmul)",
+                seconds_per_pass=dt)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(max(args.warmup, 1) if args.warmup < 2 else 2):
+        cpu_baseline(repeat=1)
+    t0 = time.perf_counter()
+    vals = [cpu_baseline(repeat=1) for _ in range(args.steps)]
+    dt = time.perf_counter() - t0
+    v = float(np.mean([c["value"] for c in vals]))
+    cb = dict(vals[0])
+    cb["value"] = v
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16xs4->f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference path; each step is one K=4096 N=4096 M=16 call"},
+        "cpu_baseline": cb,
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--small", action="store_true", help="one weight set, no extras (for profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import quant
+    lib = quant.load_library()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    sets = 1 if args.small else SETS
+    peaks = measured_peaks()
+    stream = torch.cuda.Stream(device=dev)
+    sp = stream.cuda_stream
+
+    # weights (resident), activations, outputs
+    weights = {}
+    for si, (K, N) in enumerate(DECODE_SHAPES):
+        weights[(K, N)] = [synth_packed(K, N, G, dev, 1234 + 10 * si + s) for s in range(sets)]
+    xs = {(M, K): torch.randn(M, K, device=dev, dtype=torch.float16) for M in DECODE_M for K in (4096, 16384)}
+    outs = {(M, N): torch.empty(M, N, device=dev, dtype=torch.float16) for M in DECODE_M for N in (4096, 16384)}
+
+    def launch(M, K, N, s, st):
+        qw, zs = weights[(K, N)][s]
+        r = lib.w4a16_gemm(xs[(M, K)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, N)].data_ptr(),
+                           M, N, K, G, None, 0, st)
+        if r != 0:
+            raise RuntimeError(lib.w4a16_status_str(r).decode())
+
+    calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
+    step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
+    launches_per_step = len(calls)
+
+    # one eager pass (per-device attribute set-up happens here, outside capture), then capture the step
+    with torch.cuda.stream(stream):
+        for c in calls:
+            launch(*c, sp)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for c in calls:
+            launch(*c, torch.cuda.current_stream().cuda_stream)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+    barrier()
+    t1 = time.perf_counter()
+    clocks = sampler.finish(t0, t1)
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    total_bytes = step_bytes * args.steps * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16xs4->f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "weight_sets": sets, "launches_per_step": launches_per_step,
+                   "l2": f"inputs larger than L2: {sets} rotating weight sets, {step_bytes / 1e6:.0f} MB touched per step",
+                   "timing": "CUDA graph of one step, K replays between CUDA events on the launching stream",
+                   "multi_gpu": "independent replicas, no collective" if world > 1 else "single GPU"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    line["roofline"] = {
+        "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
+        "traffic": None, "kernel": "skinny_kernel", "peak_source": f"of {peaks['source']} (copy bandwidth)",
+        "algorithmic_bytes_per_launch": step_bytes / launches_per_step,
+        "avg_launch_us": 1e3 * ms / (args.steps * launches_per_step),
+    }
+
+    if rank == 0 and not args.small:
+        line["sweep"] = decode_sweep(lib, weights, xs, outs, stream, sets, peaks)
+        line["e2e"] = e2e_host(lib, weights, dev, stream, sets, world)
+        if not args.no_prefill:
+            line["prefill"] = prefill_sweep(lib, weights, dev, stream, sets, peaks)
+        if not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(repeat=3)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def time_calls(fn, stream, iters, warm=5):
+    with torch.cuda.stream(stream):
+        for i in range(warm):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(iters):
+            fn(i)
+        e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / iters      # ms per call
+
+
+def decode_sweep(lib, weights, xs, outs, stream, sets, peaks):
+    """Per (shape, M): stream-ordered back-to-back launches rotating over the weight sets."""
+    rows = []
+    sp = stream.cuda_stream
+    for (K, N) in DECODE_SHAPES:
+        for M in DECODE_M:
+            def fn(i, M=M, K=K, N=N):
+                qw, zs = weights[(K, N)][i % sets]
+                lib.w4a16_gemm(xs[(M, K)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, N)].data_ptr(),
+                               M, N, K, G, None, 0, sp)
+            ms = time_calls(fn, stream, 40 * sets)
+            gbs = decode_bytes(M, K, N) / (ms * 1e-3) / 1e9
+            rows.append({"K": K, "N": N, "M": M, "us": 1e3 * ms, "GBps": gbs, "frac": gbs / peaks["hbm_gbs"]})
+    return rows
+
+
+def e2e_host(lib, weights, dev, stream, sets, world):
+    """The same sweep through w4a16_gemm_host: x from pinned host memory, y back to pinned host memory,
+    both copies inside the timed region; the packed weights stay resident (module state)."""
+    sp = stream.cuda_stream
+    xh = {(M, K): torch.randn(M, K).half().pin_memory() for M in DECODE_M for K in (4096, 16384)}
+    oh = {(M, N): torch.empty(M, N, dtype=torch.float16).pin_memory() for M in DECODE_M for N in (4096, 16384)}
+    xd = {k: torch.empty(k, dtype=torch.float16, device=dev) for k in xh}
+    od = {k: torch.empty(k, dtype=torch.float16, device=dev) for k in oh}
+    calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
+
+    def one(c):
+        M, K, N, s = c
+        qw, zs = weights[(K, N)][s]
+        r = lib.w4a16_gemm_host(xh[(M, K)].data_ptr(), oh[(M, N)].data_ptr(), xd[(M, K)].data_ptr(), od[(M, N)].data_ptr(),
+                                qw.data_ptr(), zs.data_ptr(), None, M, N, K, G, None, 0, sp)
+        if r != 0:
+            raise RuntimeError(lib.w4a16_status_str(r).decode())
+
+    for c in calls:
+        one(c)
+    steps = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(steps):
+        for c in calls:
+            one(c)
+    e1.record(stream)
+    stream.synchronize()
+    wall = time.perf_counter() - t0
+    step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
+    h2d = sum(M * K * 2 for (M, K, N, s) in calls)
+    d2h = sum(M * N * 2 for (M, K, N, s) in calls)
+    return {"value": step_bytes * steps / wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "steps": steps, "ms_per_step": 1e3 * wall / steps, "timer": "host wall clock around synchronous calls",
+            "device_event_ms_per_step": e0.elapsed_time(e1) / steps}
+
+
+def prefill_sweep(lib, weights, dev, stream, sets, peaks):
+    """tcgen05 GEMM: TFLOP/s = 2*M*N*K / time for M in {512, 2048, 8192} on the three shapes."""
+    rows = []
+    sp = stream.cuda_stream
+    for (K, N) in DECODE_SHAPES:
+        for M in PREFILL_M:
+            x = torch.randn(M, K, device=dev, dtype=torch.float16)
+            o = torch.empty(M, N, device=dev, dtype=torch.float16)
+
+            def fn(i, M=M, K=K, N=N, x=x, o=o):
+                qw, zs = weights[(K, N)][i % sets]
+                r = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G, None, 0, sp)
+                if r != 0:
+                    raise RuntimeError(lib.w4a16_status_str(r).decode())
+            ms = time_calls(fn, stream, 20, warm=3)
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            rows.append({"K": K, "N": N, "M": M, "ms": ms, "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                         "frac_of_nominal_2250": tf / 2250.0})
+            del x, o
+    flag = ctypes.c_int(0)
+    lib.w4a16_tc_error_flag(ctypes.byref(flag))
+    return {"rows": rows, "kernel": "tc_kernel (TMA + tcgen05.mma, A from TMEM)", "timeout_flag": flag.value,
+            "peak_tflops_measured_bf16_burst": peaks["bf16_tflops"]}
+
+
+if __name__ == "__main__":
+    main()

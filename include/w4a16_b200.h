@@ -1,0 +1,158 @@
+/*
+ * w4a16_b200 — C ABI of the B200 (sm_100a) W4A16 group-quantised linear layer.
+ *
+ * Drop-in boundary for the `quant` extension of sparklesea/sparse-quant
+ * (quantization/nvidia/kernel).  Each entry point names the reference interface it
+ * replaces.  All pointers are DEVICE pointers unless stated otherwise, all tensors are
+ * dense and row-major, `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ * stream).  Every function returns a w4a16_status (0 = success) and never throws; nothing
+ * is launched when the status is an argument error.  Launches are asynchronous.
+ *
+ * Tensor formats (identical to the reference's):
+ *   qweight       int32  [K, N/8]      TurboMind "s4_k_m8" tile order, physically
+ *                                      [K/32][N/32][32 lanes][4 words] (512 B per 32x32 tile)
+ *   zeros_scales  fp16   [K/g, 2N]     per (group, out-feature) the pair (zero + 64, scale)
+ *   x             fp16   [tokens, K]
+ *   out           fp16   [tokens, N]
+ *   bias          fp16   [N] or NULL
+ * Constraints: N % 32 == 0, K % g == 0, g in {32, 64, 128}, tokens >= 0; x, qweight,
+ * zeros_scales and out 16-byte aligned.  The tcgen05 kernel additionally needs g in {64, 128};
+ * W4A16_ALGO_AUTO falls back to the skinny kernel otherwise.
+ */
+#ifndef W4A16_B200_H_
+#define W4A16_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum w4a16_status {
+    W4A16_OK                  = 0,
+    W4A16_ERR_NULL_POINTER    = 1,  /* a required pointer is NULL */
+    W4A16_ERR_BAD_SHAPE       = 2,  /* N % 32 != 0, K % g != 0, negative size, size overflow */
+    W4A16_ERR_GROUP_SIZE      = 3,  /* "unsupported group size" (gemm_s4_f16.cu:232-234) */
+    W4A16_ERR_MISALIGNED      = 4,  /* pointer not 16-byte aligned where vector access needs it */
+    W4A16_ERR_WORKSPACE       = 5,  /* workspace missing or smaller than w4a16_workspace_bytes() */
+    W4A16_ERR_BAD_ALGO        = 6,  /* unknown algo id, or algo cannot run this shape */
+    W4A16_ERR_CUDA            = 7,  /* a CUDA runtime/driver call failed (see w4a16_last_cuda_error) */
+    W4A16_ERR_UNSUPPORTED_GPU = 8,  /* device is not compute capability 10.x */
+    W4A16_ERR_TOO_LARGE       = 9   /* size beyond a stated fixed capacity */
+} w4a16_status;
+
+/* kernel selection for w4a16_gemm_algo */
+typedef enum w4a16_algo {
+    W4A16_ALGO_AUTO   = 0,  /* tokens <= 32: skinny kernel; otherwise the tcgen05 kernel */
+    W4A16_ALGO_SKINNY = 1,  /* mma.sync skinny GEMM, cluster split-K (decode) */
+    W4A16_ALGO_TC     = 2   /* TMA + tcgen05/TMEM GEMM (prefill) */
+} w4a16_algo;
+
+/* Human readable text for a status code (static storage, never NULL). */
+const char* w4a16_status_str(int status);
+
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling
+ * thread (0 if none). */
+int w4a16_last_cuda_error(void);
+
+/*
+ * out[t, n] = fp16( sum_k fp32( dequant(qweight)[n, k] * x[t, k] ) ) (+ bias[n], fp16 add)
+ *
+ * Replaces gemm_awq_ut / Gemm_awq_pure / gemm_awq_api (kernel/gemm_quant.cu:98-122,42-96,
+ * 13-40, declared kernel/gemm_quant.h:15-17) and the fp16 bias add of WALinear.forward
+ * (test/nvidia/module/qlinear/qlinear.py:69-70), which is fused here.  Unlike the
+ * reference the launch goes to `stream`, g may be 32/64/128 and any N % 32 == 0 is
+ * accepted.  `workspace` may be NULL when w4a16_workspace_bytes() returns 0.
+ */
+int w4a16_gemm(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+               void* out, int tokens, int N, int K, int group_size,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same as w4a16_gemm with an explicit kernel choice (tests and benchmarks). */
+int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                    void* out, int tokens, int N, int K, int group_size,
+                    void* workspace, size_t workspace_bytes, void* stream, int algo);
+
+/* Scratch bytes w4a16_gemm needs for this problem (0 = none).  The reference has no
+ * workspace (the WorkSpace argument of Gemm_awq_pure, gemm_quant.cu:45, is unused). */
+size_t w4a16_workspace_bytes(int tokens, int N, int K, int group_size);
+
+/*
+ * w[n, k] = mul.ftz.f16( sub.ftz.f16( 64 + q[n,k], zero[n,k/g] + 64 ), scale[n,k/g] )
+ * written as fp16 [N, K] (the orientation of nn.Linear.weight), bit-exact with the
+ * in-kernel dequantisation of the reference (dequantize_s4_to_fp16x2_v2 + apply_Q,
+ * kernel/gemm_s4_f16/common.h:114-153,210-225).  The NVIDIA reference binds no such op;
+ * the name and argument order follow the `dequant` op of its sibling backend
+ * (quantization/tianshu/backend/pybind.cpp:12).
+ */
+int w4a16_dequant(const void* qweight, const void* zeros_scales, void* w_out,
+                  int N, int K, int group_size, void* stream);
+
+/*
+ * zeros_scales[k/g][n] = half2(zeros[n][k/g] + 64, scales[n][k/g]).
+ * Replaces transpose_merge_zeros_scales (kernel/gemm_s4_f16/format.cu:206-239,
+ * declared kernel/gemm_quant.h:19-24).  zeros, scales: fp16 [N, K/g].
+ */
+int w4a16_transpose_merge_zeros_scales(const void* zeros, const void* scales, void* zeros_scales,
+                                       int in_features, int out_features, int group_size, void* stream);
+
+/*
+ * uint8 [N, K/2] (byte = q[n,2i] << 4 | q[n,2i+1]) -> uint32 [K, N/8] AWQ nibble order.
+ * Replaces convert_ours_to_awq (format.cu:151-201, declared gemm_quant.h:26-29).
+ */
+int w4a16_convert_ours_to_awq(const void* qweight_src, void* qweight_dst,
+                              int in_features, int out_features, void* stream);
+
+/*
+ * AWQ uint32 [K, N/8] -> TurboMind tile order int32 [K, N/8].  Replaces
+ * convert_awq_to_lmdeploy -> convert_s4_k_m8 -> reformat_s4_k_m8 -> permute_u4
+ * (format.cu:135-149,90-105,66-71,24-57, declared gemm_quant.h:31-33).  Needs K % 32 == 0
+ * and N % 32 == 0.
+ */
+int w4a16_convert_awq_to_lmdeploy(const void* qweight_src, void* qweight_dst,
+                                  int in_features, int out_features, void* stream);
+
+/*
+ * The same GEMM through HOST buffers: copies x (and nothing else) host->device, runs
+ * w4a16_gemm on `stream`, copies out device->host and synchronises the stream.  The
+ * packed weights stay resident on the device, as they do in the reference's WALinear
+ * module (qlinear.py:26-34).  `x_dev`/`out_dev` are caller-provided device staging
+ * buffers of tokens*K and tokens*N fp16.  For pinned host memory the copies are
+ * asynchronous on `stream`.
+ */
+int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_dev,
+                    const void* qweight, const void* zeros_scales, const void* bias,
+                    int tokens, int N, int K, int group_size,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The tcgen05 kernel bounds every barrier wait; if one ever times out the kernel sets a
+ * per-device error word, frees its tensor memory and returns.  This reads that word
+ * (*flag = 0: no kernel on the current device ever gave up).  Synchronises the device; the
+ * first call on a device allocates the word, so make it outside stream capture.  The
+ * reference has no counterpart (it checks no CUDA error at all, gemm_s4_f16_kernel.h:136-145).
+ */
+int w4a16_tc_error_flag(int* flag);
+
+/* Debug aid: runs a one-CTA probe that writes tagged words to tensor memory with the 16-lane
+ * fragment store the tcgen05 kernel uses and reads them back lane by lane; out = uint32
+ * [128 lanes][32 columns] on the device.  tests/test_gpu_tmem.py decodes it. */
+int w4a16_debug_tmem_layout(void* out, void* stream);
+
+/* Benchmark/tuning hooks, not part of the drop-in surface (0 = automatic choice):
+ * skinny kernel: out-feature tiles per CTA (1,2,4,8) and cluster split-K (1,2,4,8);
+ * tcgen05 kernel: token tile (64,128,256). */
+void w4a16_tune_skinny(int wn, int splits);
+void w4a16_tune_tc(int tile_tokens, int split_k);
+
+/* Number of kernels this library has launched on the calling process so far. */
+unsigned long long w4a16_launch_count(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int w4a16_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_B200_H_ */

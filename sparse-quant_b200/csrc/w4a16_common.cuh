@@ -1,0 +1,117 @@
+// Shared device helpers of the W4A16 kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "w4a16_b200.h"
+
+namespace w4a16 {
+
+// ---------------------------------------------------------------------------------------------
+// Packed weight format ("s4_k_m8" tile order of the reference, cta_iterator.h:86-88):
+//   physical [K/32][N/32][lane 0..31][word 0..3]; a 32(k) x 32(n) tile is 512 contiguous bytes,
+//   16 bytes per lane.  For element (n, k) inside a tile
+//       lane   = (n % 8) * 4 + (k % 8) / 2
+//       word   = ((k / 16) % 2) * 2 + ((n / 16) % 2)
+//       nibble = (k % 2) * 4 + ((k / 8) % 2) * 2 + ((n / 8) % 2)
+//   so word (kh, nh) of a lane is the mma.m16n8k16 A fragment (rows = out-features) of the
+//   16(n) x 16(k) sub-block (nh, kh): after unpack_s4x8() h[0] = row r, k 2c..2c+1; h[1] = row
+//   r+8, same k; h[2] = row r, k+8; h[3] = row r+8, k+8   (r = lane/4, c = lane%4).
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kTileK = 32;
+constexpr int kTileN = 32;
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+    return r;
+}
+
+// Eight nibbles -> four half2 bit patterns, each half = fp16(64 + q) (0x5400 | q << 4), exact.
+// Same values as dequantize_s4_to_fp16x2_v2 (common.h:114-153): pairs are nibbles (0,4), (1,5),
+// (2,6), (3,7).
+__device__ __forceinline__ void unpack_s4x8(uint32_t w, uint32_t (&h)[4])
+{
+    constexpr uint32_t kMask = 0x00f000f0u, kMagic = 0x54005400u;
+    h[0] = lop3_and_or(w << 4, kMask, kMagic);
+    h[1] = lop3_and_or(w, kMask, kMagic);
+    h[2] = lop3_and_or(w >> 4, kMask, kMagic);
+    h[3] = lop3_and_or(w >> 8, kMask, kMagic);
+}
+
+// (t - z) * s in fp16 with flush-to-zero, two lanes at a time: bit-exact with apply_Q
+// (common.h:210-225, the non-FMA branch).
+__device__ __forceinline__ uint32_t dequant_h2(uint32_t t, uint32_t zz, uint32_t ss)
+{
+    uint32_t u, v;
+    asm("sub.ftz.f16x2 %0, %1, %2;" : "=r"(u) : "r"(t), "r"(zz));
+    asm("mul.ftz.f16x2 %0, %1, %2;" : "=r"(v) : "r"(u), "r"(ss));
+    return v;
+}
+
+// half2 (zero+64, scale) -> (zz, ss) broadcasts
+__device__ __forceinline__ void split_zs(uint32_t zs, uint32_t& zz, uint32_t& ss)
+{
+    zz = __byte_perm(zs, zs, 0x1010);
+    ss = __byte_perm(zs, zs, 0x3232);
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p)
+{
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t ldg_nc_u32(const void* p)
+{
+    uint32_t r;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-side plumbing shared by the translation units
+// ---------------------------------------------------------------------------------------------
+struct GemmArgs {
+    const __half*   x;
+    const uint32_t* qw;
+    const uint32_t* zs;    // half2 (zero+64, scale) as 32-bit words, [K/g][N]
+    const __half*   bias;  // may be null
+    __half*         out;
+    int tokens, N, K, g;
+};
+
+int  record_cuda_error(cudaError_t e);          // returns W4A16_ERR_CUDA, remembers e
+void count_launch(unsigned n = 1);
+
+int launch_skinny(const GemmArgs& a, cudaStream_t st);
+int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+size_t tc_workspace_bytes(int tokens, int N, int K, int g);
+bool tc_supported(int tokens, int N, int K, int g);
+
+}  // namespace w4a16

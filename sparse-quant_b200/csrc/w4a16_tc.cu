@@ -1,0 +1,442 @@
+// Prefill kernel: W4A16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+//   out[t, n] = fp16( sum_k fp32( dq(W)[n, k] * x[t, k] ) ) (+ bias[n])
+//
+// Replaces the large-token instantiations of gemm_s4_f16_nn (gemm_template.h:358-464 of the
+// reference: mma.sync + cp.async + ldmatrix, dequantisation re-done in the MMA issue slots).
+// Role assignment follows the packed format: the weights are the MMA "A" operand (M = 128
+// out-features per CTA tile), the activations are "B" (N = 64/128/256 tokens), the fp32
+// accumulator D[out-feature lane][token column] lives in tensor memory.
+//
+// One persistent CTA per SM, 192 threads, warp specialised:
+//   warp 4   TMA producer: per 64-k step one tensor copy of the activation tile (128-byte
+//            swizzle, K-major) plus plain bulk copies of the packed weight tiles (a k-tile row
+//            of the format is contiguous) and of the group's (zero, scale) row; all complete on
+//            one mbarrier per stage.  No cluster fan-out is used anywhere.
+//   warps0-3 dequantisers: read 16 B per lane per 32x32 tile from shared memory, expand the
+//            nibbles in registers, (t - z) * s with sub.ftz/mul.ftz (bit-exact with the
+//            reference), and write the fp16 result straight into tensor memory with
+//            tcgen05.st.16x128b - the packed layout is already that fragment order - so the
+//            dequantised weights never touch shared memory.
+//   warp 5   MMA issuer: tcgen05.mma kind::f16 with A from tensor memory and B from the
+//            swizzled shared-memory tile, four K=16 instructions per stage; tcgen05.commit
+//            releases the stage and, after the last step, publishes the accumulator.
+//   warps0-3 epilogue (after their last dequant step of the tile): tcgen05.ld the accumulator,
+//            fp32 -> fp16, bias add, transposed store to out[token, out-feature].
+// Every mbarrier wait is bounded; on a timeout the CTA raises an error word in global memory,
+// drains and frees its tensor memory, and returns.
+#include <cuda.h>
+
+#include "w4a16_common.cuh"
+#include "w4a16_sm100.cuh"
+
+namespace w4a16 {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 packed tiles)
+constexpr int kBlockK   = 64;                  // k per stage (2 packed tiles)
+constexpr int kThreads  = 192;
+constexpr int kTmemCols = 512;
+constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;   // 0.4 s: far above any legitimate wait
+
+template <int TOK>
+struct TcCfg {
+    static constexpr int kStages   = TOK == 256 ? 4 : (TOK == 128 ? 6 : 9);   // > 113 KB each: one CTA per SM
+    static constexpr int kXBytes   = TOK * kBlockK * 2;
+    static constexpr int kWBytes   = 2 * 4 * 512;
+    static constexpr int kStageBytes = kXBytes + kWBytes + 1024;     // zs padded to keep 1024-B alignment
+    static constexpr int kACol     = TOK;                             // first TMEM column of the A ring
+    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/;
+    static_assert(kACol + 32 * kStages <= kTmemCols, "TMEM budget");
+};
+
+struct TcParams {
+    const uint4*    qw;
+    const uint32_t* zs;
+    const __half*   bias;
+    __half*         out;
+    int*            error;          // device word, set non-zero on a wait timeout
+    int tokens, N, K, g;
+    int n_blocks, t_blocks;
+};
+
+template <int TOK>
+__global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p)
+{
+    using Cfg = TcCfg<TOK>;
+    constexpr int S = Cfg::kStages;
+    extern __shared__ unsigned char smem_raw[];
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + S * Cfg::kStageBytes;
+    // barrier layout (8 B each): full[S], afull[S], empty[S], dfull, dempty ; then tmem ptr, abort flag
+    auto full_bar  = [&](int s) { return bar_base + 8u * s; };
+    auto afull_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
+    const uint32_t dfull_bar = bar_base + 8u * (3 * S), dempty_bar = bar_base + 8u * (3 * S + 1);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S * Cfg::kStageBytes + 8 * (3 * S + 2));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(afull_bar(s), 4);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(dfull_bar, 1);
+        mbar_init(dempty_bar, 4);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 4 && lane == 0) prefetch_tmap(&x_map);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_tiles = p.N / kTileN;
+    const int k_steps = p.K / kBlockK;
+    const int total_tiles = p.n_blocks * p.t_blocks;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
+                const int nb_tiles = min(4, n_tiles - nb * 4);
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWaitBudgetNs);
+                    if (!ok) break;
+                    const uint32_t st = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t w_bytes = nb_tiles * 512u, zs_bytes = nb_tiles * 128u;
+                    mbar_arrive_expect_tx(full_bar(stage), Cfg::kXBytes + 2 * w_bytes + zs_bytes);
+                    tma_load_2d(st, &x_map, ks * kBlockK, tb * TOK, full_bar(stage));
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        bulk_load(st + Cfg::kXBytes + j * 2048, p.qw + ((size_t)(ks * 2 + j) * n_tiles + nb * 4) * 32,
+                                  w_bytes, full_bar(stage));
+                    const int kg = (ks * kBlockK) / p.g;
+                    bulk_load(st + Cfg::kXBytes + Cfg::kWBytes, p.zs + (size_t)kg * p.N + nb * kBlockN, zs_bytes, full_bar(stage));
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // give copies already in flight time to land before the CTA releases its shared memory
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000) { }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16_m128(TOK);
+            int stage = 0; uint32_t phase = 0, dphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                ok = mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs);   // epilogue drained D
+                if (!ok) break;
+                tc_fence_after_sync();
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs) &&
+                         mbar_wait(afull_bar(stage), phase, abort_flag, kWaitBudgetNs);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t bdesc = smem_desc_sw128(smem_base + stage * Cfg::kStageBytes);
+                    const uint32_t a_tmem = tmem_base + Cfg::kACol + 32 * stage;
+#pragma unroll
+                    for (int kk = 0; kk < kBlockK / 16; ++kk)
+                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    tc_commit(empty_bar(stage));
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(dfull_bar);
+                dphase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------ dequant + epilogue (warps 0..3) ------------------------------
+        int stage = 0; uint32_t phase = 0, dphase = 0;
+        bool ok = true;
+        const int r = lane >> 2;
+        const uint32_t lane_field = (uint32_t)(warp * 32) << 16;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
+            const bool has_tile = nb * 4 + warp < n_tiles;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs));
+                if (!ok) break;
+                if (has_tile) {
+                    const unsigned char* st = smem + stage * Cfg::kStageBytes;
+                    const uint4* wq = reinterpret_cast<const uint4*>(st + Cfg::kXBytes);
+                    const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + warp * 32 + r;
+                    const uint4 q0 = wq[warp * 32 + lane], q1 = wq[128 + warp * 32 + lane];
+                    const uint32_t words[2][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}};
+#pragma unroll
+                    for (int nh = 0; nh < 2; ++nh) {
+                        uint32_t z0, s0, z1, s1;
+                        split_zs(zsp[nh * 16], z0, s0);
+                        split_zs(zsp[nh * 16 + 8], z1, s1);
+                        uint32_t a[16];
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+#pragma unroll
+                            for (int kh = 0; kh < 2; ++kh) {
+                                uint32_t h[4];
+                                unpack_s4x8(words[j][kh * 2 + nh], h);
+                                uint32_t* d = a + j * 8 + kh * 4;
+                                d[0] = dequant_h2(h[0], z0, s0);
+                                d[1] = dequant_h2(h[1], z1, s1);
+                                d[2] = dequant_h2(h[2], z0, s0);
+                                d[3] = dequant_h2(h[3], z1, s1);
+                            }
+                        tmem_st_16x128b_x8(tmem_base + lane_field + ((uint32_t)(nh * 16) << 16) + Cfg::kACol + 32 * stage, a);
+                    }
+                    tmem_wait_st();
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(afull_bar(stage));
+                if (++stage == S) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) break;
+
+            // epilogue: thread = out-feature (TMEM lane), registers = tokens
+            ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, dphase, abort_flag, kWaitBudgetNs));
+            if (!ok) break;
+            dphase ^= 1u;
+            tc_fence_after_sync();
+            const int n = nb * kBlockN + warp * 32 + lane;
+            const bool n_ok = n < p.N;
+            const __half bias = (p.bias && n_ok) ? p.bias[n] : __half();
+            const int tok0 = tb * TOK;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TOK; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
+                tmem_wait_ld();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int t = tok0 + c0 + j;
+                        if (t < p.tokens) {
+                            __half h = __float2half_rn(__uint_as_float(v[j]));
+                            if (p.bias) h = __hadd(h, bias);
+                            p.out[(size_t)t * p.N + n] = h;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dempty_bar);
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) atomicExch(p.error, 1);
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+
+// Hardware self-check of the tensor-memory fragment mapping the dequantisers rely on: every warp
+// stores tagged words with tcgen05.st.16x128b.x8 (both 16-lane halves) and reads its 32 lanes back
+// with tcgen05.ld.32x32b.x32, which has the trivial mapping (thread i = lane i, register = column).
+__global__ void __launch_bounds__(128, 1) tmem_layout_probe_kernel(uint32_t* out)
+{
+    __shared__ uint32_t slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&slot), 32);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t base = slot;
+    const uint32_t lane_field = (uint32_t)(warp * 32) << 16;
+    for (int nh = 0; nh < 2; ++nh) {
+        uint32_t r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = ((uint32_t)warp << 24) | ((uint32_t)nh << 20) | ((uint32_t)lane << 8) | (uint32_t)j;
+        tmem_st_16x128b_x8(base + lane_field + ((uint32_t)(nh * 16) << 16), r);
+    }
+    tmem_wait_st();
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(base + lane_field, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 32; ++c) out[(warp * 32 + lane) * 32 + c] = v[c];
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(base, 32);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    }
+    return fn;
+}
+
+int g_force_tok = 0;
+
+int pick_tok(int tokens, int N, int K)
+{
+    if (g_force_tok == 64 || g_force_tok == 128 || g_force_tok == 256) return g_force_tok;
+    const int n_blocks = (N + kBlockN - 1) / kBlockN;
+    const long long k_steps = K / kBlockK;
+    int best = 256;
+    long long best_cost = -1;
+    const int cands[3] = {256, 128, 64};
+    for (int i = 0; i < 3; ++i) {
+        const int t = cands[i];
+        const long long tiles = (long long)n_blocks * ((tokens + t - 1) / t);
+        const long long waves = (tiles + 147) / 148;
+        const long long step = 2 * t > 240 ? 2 * t : 240;            // clocks: MMA vs dequant bound
+        const long long cost = waves * (k_steps * step + 6 * t + 2000);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = t; }
+    }
+    return best;
+}
+
+// per-device error word (allocated once; the kernels only ever write 1 into it)
+int* error_word()
+{
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+        if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return nullptr;
+        words[dev] = p;
+    }
+    return words[dev];
+}
+
+template <int TOK>
+int launch_tok(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t st)
+{
+    static int configured[64] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev >= 64 || !configured[dev]) {
+        e = cudaFuncSetAttribute(tc_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcCfg<TOK>::kSmemBytes);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev < 64) configured[dev] = 1;
+    }
+    tc_kernel<TOK><<<grid, kThreads, TcCfg<TOK>::kSmemBytes, st>>>(map, p);
+    count_launch();
+    e = cudaGetLastError();
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
+}  // namespace
+
+void tc_force_config(int tile_tokens, int /*split_k*/) { g_force_tok = tile_tokens; }
+
+bool tc_supported(int tokens, int N, int K, int g)
+{
+    return tokens > 0 && (g == 64 || g == 128) && (K % kBlockK) == 0 && (N % kTileN) == 0;
+}
+
+size_t tc_workspace_bytes(int, int, int, int) { return 0; }
+
+int tc_error_state(int* host_out)
+{
+    int* w = error_word();
+    if (!w) return W4A16_ERR_CUDA;
+    cudaError_t e = cudaMemcpy(host_out, w, sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
+int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
+{
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return W4A16_ERR_CUDA;
+    int* err = error_word();
+    if (!err) return W4A16_ERR_CUDA;
+    const int tok = pick_tok(a.tokens, a.N, a.K);
+
+    CUtensorMap map;
+    const cuuint64_t dims[2]    = {(cuuint64_t)a.K, (cuuint64_t)a.tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * sizeof(__half)};
+    const cuuint32_t box[2]     = {(cuuint32_t)kBlockK, (cuuint32_t)tok};
+    const cuuint32_t estr[2]    = {1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.x, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue);
+
+    TcParams p;
+    p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out; p.error = err;
+    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.g = a.g;
+    p.n_blocks = (a.N + kBlockN - 1) / kBlockN;
+    p.t_blocks = (a.tokens + tok - 1) / tok;
+    const long long tiles = (long long)p.n_blocks * p.t_blocks;
+    int sms = 148;
+    {
+        static int cached[64] = {0};
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev < 64) {
+            if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+            if (cached[dev] > 0) sms = cached[dev];
+        }
+    }
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    switch (tok) {
+        case 256: return launch_tok<256>(map, p, grid, st);
+        case 128: return launch_tok<128>(map, p, grid, st);
+        default:  return launch_tok<64>(map, p, grid, st);
+    }
+}
+
+}  // namespace w4a16
+
+// Reads (and leaves set) the device error word the tcgen05 kernel raises when one of its
+// bounded waits times out.  Synchronises the device.  *flag = 0 means no kernel ever gave up.
+// Debug aid: fills out[128][32] (device, uint32) with the tags read back by the probe kernel above.
+extern "C" int w4a16_debug_tmem_layout(void* out, void* stream)
+{
+    if (!out) return W4A16_ERR_NULL_POINTER;
+    w4a16::tmem_layout_probe_kernel<<<1, 128, 0, (cudaStream_t)stream>>>((uint32_t*)out);
+    w4a16::count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? W4A16_OK : w4a16::record_cuda_error(e);
+}
+
+extern "C" int w4a16_tc_error_flag(int* flag)
+{
+    if (!flag) return W4A16_ERR_NULL_POINTER;
+    return w4a16::tc_error_state(flag);
+}

@@ -1,0 +1,217 @@
+"""`quant` — drop-in for the reference's CUDA extension of the same name, on B200.
+
+The reference builds a pybind11 module `quant` (quantization/nvidia/kernel/pybind.cpp:7-12)
+with four functions; this package exposes the same four names with the same positional
+arguments, tensor formats and error behaviour (RuntimeError on bad arguments, as TORCH_CHECK
+raises in kernel/utils.h:10-16), plus `dequant` (named after the op of the reference's
+sibling backend, quantization/tianshu/backend/pybind.cpp:12).
+
+The work is done by hand-written sm_100a kernels behind a C ABI (include/w4a16_b200.h,
+libw4a16_b200.so next to this file) called through ctypes; torch only provides device
+memory and the current stream.  There is no CPU path and no fallback: importing works
+anywhere (so the host logic can be tested), calling a function without the built library
+or without a B200 raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+__all__ = [
+    "gemm_awq_ut", "transpose_merge_zeros_scales", "convert_ours_to_awq", "convert_awq_to_lmdeploy",
+    "dequant", "gemm_awq_bias", "library_path", "load_library", "launch_count",
+]
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_NAME = "libw4a16_b200.so"
+_lib = None
+
+ALGO_AUTO, ALGO_SKINNY, ALGO_TC = 0, 1, 2
+
+# every symbol include/w4a16_b200.h declares: name -> (restype, argtypes)
+_vp, _ci, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+C_ABI = {
+    "w4a16_status_str": (ctypes.c_char_p, [_ci]),
+    "w4a16_last_cuda_error": (_ci, []),
+    "w4a16_gemm": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
+    "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
+    "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
+    "w4a16_dequant": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "w4a16_transpose_merge_zeros_scales": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "w4a16_convert_ours_to_awq": (_ci, [_vp, _vp, _ci, _ci, _vp]),
+    "w4a16_convert_awq_to_lmdeploy": (_ci, [_vp, _vp, _ci, _ci, _vp]),
+    "w4a16_gemm_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
+    "w4a16_launch_count": (ctypes.c_ulonglong, []),
+    "w4a16_version": (_ci, []),
+    "w4a16_tc_error_flag": (_ci, [ctypes.POINTER(_ci)]),
+    "w4a16_debug_tmem_layout": (_ci, [_vp, _vp]),
+    "w4a16_tune_skinny": (None, [_ci, _ci]),
+    "w4a16_tune_tc": (None, [_ci, _ci]),
+}
+
+
+def library_path() -> str:
+    return os.path.join(_HERE, _LIB_NAME)
+
+
+def load_library() -> ctypes.CDLL:
+    """Load the C-ABI library (built by sparse-quant_b200/build.py).  Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{_LIB_NAME} is not built (expected at {path}); run `python sparse-quant_b200/build.py`. "
+                "There is no CPU or PyTorch fallback for the W4A16 kernels.")
+        lib = ctypes.CDLL(path)
+        for name, (res, args) in C_ABI.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load_library()
+        msg = lib.w4a16_status_str(status).decode()
+        extra = f" (cudaError {lib.w4a16_last_cuda_error()})" if status == 7 else ""
+        raise RuntimeError(f"{what}: {msg}{extra}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_tensor(t, name, *, dtype=None, dims=None):
+    _need(isinstance(t, torch.Tensor), f"{name} must be a torch.Tensor")
+    _need(t.is_cuda, f"Tensor {name} must be on CUDA")
+    _need(t.is_contiguous(), f"Tensor {name} must be contiguous")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"Tensor {name} must have dtype ({dtype})")
+    if dims is not None:
+        _need(t.dim() == dims, f"Tensor {name} must have dimension number ({dims})")
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(load_library().w4a16_launch_count())
+
+
+def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None):
+    """gemm_awq_ut with the fp16 bias add of WALinear.forward fused into the kernel epilogue.
+
+    I fp16 [b, s, K] (CUDA, contiguous); W int32 [K, N/8] tile-ordered; W_zeros_scales fp16
+    [K/g, 2N]; bias fp16 with N elements or None.  Returns fp16 [b, s, N].
+    """
+    _check_tensor(I, "I", dtype=torch.float16, dims=3)
+    _check_tensor(W, "W", dims=2)
+    _check_tensor(W_zeros_scales, "W_zeros_scales", dtype=torch.float16, dims=2)
+    b, s, K = I.shape
+    N = int(N)
+    group_size = int(group_size)
+    _need(W.device == I.device and W_zeros_scales.device == I.device, "all tensors must be on the same device")
+    _need(group_size > 0 and N > 0, "unsupported group size" if group_size <= 0 else "N must be positive")
+    _need(W.numel() * W.element_size() * 2 == K * N, f"Tensor W must hold K*N/2 = {K * N // 2} bytes of packed int4")
+    _need(K % group_size == 0 and W_zeros_scales.numel() == (K // group_size) * N * 2,
+          "Tensor W_zeros_scales must have K/group_size * 2N elements")
+    if bias is not None:
+        _check_tensor(bias, "bias", dtype=torch.float16)
+        _need(bias.numel() == N and bias.device == I.device, "Tensor bias must have N elements on the same device")
+    if out is None:
+        out = torch.empty((b, s, N), dtype=torch.float16, device=I.device)
+    else:
+        _check_tensor(out, "O", dtype=torch.float16, dims=3)
+        _need(tuple(out.shape) == (b, s, N) and out.device == I.device, "Tensor O must have shape [b, s, N]")
+    lib = load_library()
+    tokens = b * s
+    with torch.cuda.device(I.device):
+        ws_bytes = lib.w4a16_workspace_bytes(tokens, N, K, group_size)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=I.device) if ws_bytes else None
+        st = lib.w4a16_gemm_algo(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                 bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                 tokens, N, K, group_size,
+                                 ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo))
+    _check(st, "gemm_awq_ut")
+    return out
+
+
+def gemm_awq_ut(I, W, W_zeros_scales, M: int, N: int, K: int, group_size: int):
+    """O[b, s, :] = I[b, s, :] @ dequant(W, W_zeros_scales)^T, fp16.
+
+    Same signature as the reference's gemm_awq_ut (kernel/gemm_quant.h:15-17,
+    kernel/gemm_quant.cu:98-122).  As there, `M` and `K` are accepted and ignored: the token
+    count and K come from `I` (gemm_quant.cu:85-87); `I` must be 3-D.  Launches on torch's
+    current stream (the reference uses the legacy default stream).
+    """
+    return gemm_awq_bias(I, W, W_zeros_scales, None, N, group_size)
+
+
+def transpose_merge_zeros_scales(zeros, scales, zeros_scales, in_features: int, out_features: int, group_size: int):
+    """zeros_scales[k/g, 2n:2n+2] = (zeros[n, k/g] + 64, scales[n, k/g]); in place, returns None.
+    Reference: kernel/gemm_s4_f16/format.cu:206-239."""
+    _check_tensor(zeros, "zeros", dtype=torch.float16)
+    _check_tensor(scales, "scales", dtype=torch.float16)
+    _check_tensor(zeros_scales, "zeros_scales", dtype=torch.float16)
+    _need(int(group_size) > 0 and in_features % int(group_size) == 0, "in_features must be a multiple of group_size")
+    groups = in_features // int(group_size)
+    _need(zeros.numel() == out_features * groups and scales.numel() == out_features * groups,
+          "zeros/scales must have out_features * in_features/group_size elements")
+    _need(zeros_scales.numel() == groups * out_features * 2, "zeros_scales must have in_features/group_size * 2*out_features elements")
+    with torch.cuda.device(zeros.device):
+        st = load_library().w4a16_transpose_merge_zeros_scales(
+            zeros.data_ptr(), scales.data_ptr(), zeros_scales.data_ptr(), int(in_features), int(out_features),
+            int(group_size), _stream(zeros))
+    _check(st, "transpose_merge_zeros_scales")
+
+
+def convert_ours_to_awq(qweight_src, qweight_dst, in_features: int, out_features: int):
+    """uint8 [N, K/2] -> AWQ-ordered words written into qweight_dst (uint8 [K, N/2], i.e. uint32
+    [K, N/8]); in place, returns None.  Reference: kernel/gemm_s4_f16/format.cu:151-201."""
+    _check_tensor(qweight_src, "qweight_src", dtype=torch.uint8)
+    _check_tensor(qweight_dst, "qweight_dst")
+    _need(qweight_src.numel() == in_features * out_features // 2, "qweight_src must have out_features * in_features/2 bytes")
+    _need(qweight_dst.numel() * qweight_dst.element_size() == in_features * out_features // 2,
+          "qweight_dst must have in_features * out_features/2 bytes")
+    with torch.cuda.device(qweight_src.device):
+        st = load_library().w4a16_convert_ours_to_awq(qweight_src.data_ptr(), qweight_dst.data_ptr(),
+                                                      int(in_features), int(out_features), _stream(qweight_src))
+    _check(st, "convert_ours_to_awq")
+
+
+def convert_awq_to_lmdeploy(qweight, qweight_dst, in_features: int, out_features: int):
+    """AWQ words -> tile-ordered int32 [K, N/8] (the `weight` buffer the GEMM reads); in place,
+    returns None.  Reference: kernel/gemm_s4_f16/format.cu:135-149,24-71."""
+    _check_tensor(qweight, "qweight")
+    _check_tensor(qweight_dst, "qweight_dst")
+    nbytes = in_features * out_features // 2
+    _need(qweight.numel() * qweight.element_size() == nbytes, "qweight must have in_features * out_features/2 bytes")
+    _need(qweight_dst.numel() * qweight_dst.element_size() == nbytes, "qweight_dst must have in_features * out_features/2 bytes")
+    with torch.cuda.device(qweight.device):
+        st = load_library().w4a16_convert_awq_to_lmdeploy(qweight.data_ptr(), qweight_dst.data_ptr(),
+                                                          int(in_features), int(out_features), _stream(qweight))
+    _check(st, "convert_awq_to_lmdeploy")
+
+
+def dequant(W, W_zeros_scales, N: int, K: int, group_size: int):
+    """Packed tensors -> fp16 [N, K] weight, bit-exact with the reference's in-kernel dequantisation
+    (kernel/gemm_s4_f16/common.h:114-153,210-225)."""
+    _check_tensor(W, "W", dims=2)
+    _check_tensor(W_zeros_scales, "W_zeros_scales", dtype=torch.float16, dims=2)
+    _need(W.numel() * W.element_size() * 2 == K * N, "Tensor W must hold K*N/2 bytes of packed int4")
+    _need(int(group_size) > 0 and K % int(group_size) == 0 and
+          W_zeros_scales.numel() == (K // int(group_size)) * N * 2, "Tensor W_zeros_scales must have K/group_size * 2N elements")
+    out = torch.empty((N, K), dtype=torch.float16, device=W.device)
+    with torch.cuda.device(W.device):
+        st = load_library().w4a16_dequant(W.data_ptr(), W_zeros_scales.data_ptr(), out.data_ptr(), int(N), int(K),
+                                          int(group_size), _stream(W))
+    _check(st, "dequant")
+    return out

@@ -1,0 +1,63 @@
+"""WALinear — the W4A16 linear module (plugin boundary, Python side).
+
+Same constructor arguments, buffers and state-dict keys as the reference's WALinear
+(test/nvidia/module/qlinear/qlinear.py:10-99): `weight` int32 [K, N*w_bit/32] in tile order,
+`zeros_scales` fp16 [K/g, 2N], `bias` fp16 [1, N] or None — so a state dict saved by the
+reference loads here and vice versa.  forward() differs only in that the bias add is fused
+into the kernel epilogue (one launch instead of two) and the launch goes to the current stream.
+"""
+import torch
+from torch import nn
+
+from quant import gemm_awq_bias
+
+from .quant_dequant import quant_lmdeploy
+
+
+class WALinear(nn.Module):
+    def __init__(self, in_features, out_features, w_config=None, a_config=None, w_bit=4, a_bit=16,
+                 group_size=128, bias=True, quantize_output=False, dev="cuda", dtype=torch.int):
+        super().__init__()
+        if w_bit != 4:
+            raise NotImplementedError("WALinear: only w_bit=4 (the W4A16 path) is built")
+        self.in_features = in_features
+        self.out_features = out_features
+        self.w_config = w_config
+        self.a_config = a_config
+        self.w_bit = w_bit
+        self.a_bit = a_bit
+        self.group_size = group_size
+        self.register_buffer("zeros_scales", torch.zeros(in_features // group_size, out_features * 2,
+                                                          dtype=torch.float16, device=dev))
+        self.register_buffer("weight", torch.zeros(in_features, out_features * w_bit // 32, dtype=dtype, device=dev))
+        if bias:
+            self.register_buffer("bias", torch.zeros((1, out_features), dtype=torch.float16, device=dev))
+        else:
+            self.register_buffer("bias", None)
+
+    @torch.no_grad()
+    def forward(self, x):
+        """x fp16 [..., K] -> fp16 [..., N].  The reference requires 3-D input (gemm_quant.cu:73);
+        2-D and >3-D inputs are viewed as [1, tokens, K] here."""
+        shape = x.shape
+        x3 = x if x.dim() == 3 else x.reshape(1, -1, shape[-1])
+        if not x3.is_contiguous():
+            x3 = x3.contiguous()
+        y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size)
+        return y if x.dim() == 3 else y.reshape(*shape[:-1], self.out_features)
+
+    @staticmethod
+    def from_float(module, w_config, a_config=None, quantize_output=False):
+        """nn.Linear (fp16, CUDA) -> WALinear; w_config = {"n_bit": 4, "group_size": g} (reference :74-89)."""
+        assert isinstance(module, nn.Linear)
+        new = WALinear(module.in_features, module.out_features, w_config, a_config, w_bit=w_config["n_bit"],
+                       group_size=w_config["group_size"], bias=module.bias is not None,
+                       quantize_output=quantize_output, dev=module.weight.device, dtype=torch.int)
+        new.weight, new.zeros_scales, _ = quant_lmdeploy(module.weight.data, module.in_features, module.out_features,
+                                                         group_size=w_config["group_size"], n_bit=w_config["n_bit"])
+        if module.bias is not None:
+            new.bias = module.bias.data.to(torch.float16).unsqueeze(0).contiguous()
+        return new
+
+    def __repr__(self):
+        return "W{}A{}Linear({}, {})".format(self.w_bit, self.a_bit, self.in_features, self.out_features)

@@ -1,0 +1,232 @@
+"""Parity of the two GEMM kernels against the CPU oracle (through the Python shim, i.e. the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import check_gemm_tolerance, make_packed, make_x, to_dev
+
+pytestmark = pytest.mark.gpu
+
+_cache = {}
+
+
+def packed(N, K, g):
+    key = (N, K, g)
+    if key not in _cache:
+        _cache[key] = make_packed(N, K, g, seed=1234 + N % 97 + K % 89)
+    return _cache[key]
+
+
+def run(M, N, K, g, algo, bias=False, seed=4321):
+    import quant
+    p = packed(N, K, g)
+    qw, zs = to_dev(p)
+    x = make_x(M, K, seed)
+    b = None
+    if bias:
+        gen = torch.Generator().manual_seed(5)
+        b = (torch.randn(1, N, generator=gen) * 0.02).half()
+    out = quant.gemm_awq_bias(x.cuda(), qw, zs, None if b is None else b.cuda(), N, g, algo=algo)
+    torch.cuda.synchronize()
+    ref = oracle.gemm_f16(x, p["w_deq"], None if b is None else b)
+    assert out.shape == (1, M, N)
+    return check_gemm_tolerance(out[0], ref.astype(np.float32), x, p["w_deq"], K)
+
+
+SKINNY_SHAPES = [(64, 128, 128), (96, 256, 64), (32, 32, 32), (4096, 1024, 128), (1376, 1408, 64), (512, 4096, 128),
+                 (4096, 512, 128), (160, 1344, 64)]
+
+
+@pytest.mark.parametrize("N,K,g", SKINNY_SHAPES)
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32])
+def test_skinny_small_tokens(N, K, g, M):
+    run(M, N, K, g, algo=1, bias=(M % 2 == 0))
+
+
+@pytest.mark.parametrize("M", [33, 100, 257])
+def test_skinny_many_tokens_fallback(M):
+    run(M, 256, 512, 128, algo=1, bias=True)
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 16384), (16384, 4096)])
+@pytest.mark.parametrize("M", [1, 16])
+def test_skinny_opt_shapes(K, N, M):
+    run(M, N, K, 128, algo=1)
+
+
+@pytest.mark.parametrize("wn,splits", [(1, 1), (1, 8), (2, 4), (4, 2), (8, 1), (8, 8), (2, 1)])
+def test_skinny_every_decomposition(wn, splits):
+    import quant
+    lib = quant.load_library()
+    try:
+        lib.w4a16_tune_skinny(wn, splits)
+        run(5, 256, 2048, 128, algo=1, bias=True)
+        run(16, 96, 1344, 64, algo=1)
+    finally:
+        lib.w4a16_tune_skinny(0, 0)
+
+
+def test_identity_trick_reads_back_the_dequantised_weight():
+    """x = I  =>  out[k, n] = w[n, k] exactly (one product, fp32 -> fp16 is exact for an fp16 value)."""
+    import quant
+    N, K, g = 96, 256, 64
+    p = packed(N, K, g)
+    qw, zs = to_dev(p)
+    eye = torch.eye(K, dtype=torch.float16, device="cuda").unsqueeze(0)
+    for algo in (1, 2):
+        out = quant.gemm_awq_bias(eye, qw, zs, None, N, g, algo=algo)
+        got = out[0].t().contiguous().cpu().numpy().view(np.uint16).copy()
+        exp = p["w_deq"].view(np.uint16).copy()
+        got[(got & 0x7FFF) == 0] = 0
+        exp[(exp & 0x7FFF) == 0] = 0
+        assert np.array_equal(got, exp), f"algo {algo}"
+
+
+TC_SHAPES = [(128, 128, 128), (128, 256, 64), (256, 512, 128), (96, 256, 64), (1376, 1408, 64), (4096, 1024, 128)]
+
+
+@pytest.mark.parametrize("N,K,g", TC_SHAPES)
+@pytest.mark.parametrize("M", [33, 64, 100, 128, 200, 256, 300, 511, 513])
+def test_tc_parity(N, K, g, M):
+    run(M, N, K, g, algo=2, bias=(M % 2 == 1))
+    import quant
+    flag = __import__("ctypes").c_int(-1)
+    assert quant.load_library().w4a16_tc_error_flag(flag) == 0 and flag.value == 0
+
+
+@pytest.mark.parametrize("tile", [64, 128, 256])
+def test_tc_every_token_tile(tile):
+    import quant
+    lib = quant.load_library()
+    try:
+        lib.w4a16_tune_tc(tile, 0)
+        run(300, 384, 1024, 128, algo=2, bias=True)
+        run(1, 128, 128, 128, algo=2)
+    finally:
+        lib.w4a16_tune_tc(0, 0)
+
+
+def test_tc_bert_ffn_up_config():
+    """BASELINE config 1: M=512 (4 x 128), K=1024, N=4096, g=128."""
+    run(512, 4096, 1024, 128, algo=0, bias=True)
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 16384), (16384, 4096)])
+def test_tc_opt_shapes_linearity(K, N):
+    """Full-size property check (the oracle would take minutes): f(x1 + x2) ~= f(x1) + f(x2) and
+    agreement with an fp16 cuBLAS matmul on the bit-exact dequantised weight."""
+    import quant
+    g, M = 128, 2048
+    gen = torch.Generator().manual_seed(N + K)
+    w = (torch.randn(N, K, generator=gen) * 0.02).half().cuda()
+    from w4a16 import quant_lmdeploy
+    qw, zs, _ = quant_lmdeploy(w, K, N, g, 4)
+    wd = quant.dequant(qw, zs, N, K, g)
+    x = torch.randn(1, M, K, generator=gen).half().cuda()
+    out = quant.gemm_awq_bias(x, qw, zs, None, N, g, algo=2)
+    ref = (x[0].float() @ wd.float().t())
+    fro = ((out[0].float() - ref).norm() / ref.norm()).item()
+    assert fro <= 2e-3, fro
+    err = (out[0].float() - ref).abs().max().item()
+    assert err <= 1e-2 * x.abs().max().item() * (K ** 0.5) * wd.abs().max().item()
+
+
+def test_api_contract_errors():
+    import quant
+    p = packed(64, 128, 128)
+    qw, zs = to_dev(p)
+    x = make_x(4, 128).cuda()
+    with pytest.raises(RuntimeError, match="dimension"):
+        quant.gemm_awq_ut(x[0], qw, zs, 4, 64, 128, 128)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        quant.gemm_awq_ut(x.transpose(1, 2).contiguous().transpose(1, 2), qw, zs, 4, 64, 128, 128)
+    with pytest.raises(RuntimeError, match="dtype"):
+        quant.gemm_awq_ut(x.float(), qw, zs, 4, 64, 128, 128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        quant.gemm_awq_ut(x.cpu(), qw, zs, 4, 64, 128, 128)
+    with pytest.raises(RuntimeError):
+        quant.gemm_awq_ut(x, qw, zs, 4, 64, 128, 100)          # unsupported group size
+    with pytest.raises(RuntimeError):
+        quant.gemm_awq_ut(x, qw, zs, 4, 48, 128, 128)          # N not a multiple of 32 / wrong sizes
+    # M and K arguments are ignored like in the reference (gemm_quant.cu:85-87)
+    a = quant.gemm_awq_ut(x, qw, zs, 12345, 64, 999, 128)
+    b = quant.gemm_awq_ut(x, qw, zs, 4, 64, 128, 128)
+    assert torch.equal(a, b)
+
+
+def test_output_canaries_and_determinism():
+    """Nothing is written outside [tokens, N]; repeated calls give identical bits."""
+    import quant
+    lib = quant.load_library()
+    N, K, g = 160, 1344, 64
+    p = packed(N, K, g)
+    qw, zs = to_dev(p)
+    for M, algo in [(5, 1), (16, 1), (70, 2), (300, 2)]:
+        x = make_x(M, K).cuda()
+        big = torch.full((M + 2, N), 777.0, dtype=torch.float16, device="cuda")
+        out = big[1:M + 1]
+        st = lib.w4a16_gemm_algo(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, out.data_ptr(), M, N, K, g,
+                                 None, 0, torch.cuda.current_stream().cuda_stream, algo)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert (big[0] == 777.0).all() and (big[M + 1] == 777.0).all()
+        again = quant.gemm_awq_bias(x, qw, zs, None, N, g, algo=algo)
+        assert torch.equal(again[0], out)
+
+
+def test_non_default_stream_and_graph_replay():
+    import quant
+    N, K, g = 512, 4096, 128
+    p = packed(N, K, g)
+    qw, zs = to_dev(p)
+    for M, algo in [(8, 1), (256, 2)]:
+        x = make_x(M, K).cuda()
+        eager = quant.gemm_awq_bias(x, qw, zs, None, N, g, algo=algo)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            side = quant.gemm_awq_bias(x, qw, zs, None, N, g, algo=algo)
+        s.synchronize()
+        assert torch.equal(eager, side)
+        out = torch.empty_like(eager)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            quant.gemm_awq_bias(x, qw, zs, None, N, g, algo=algo, out=out)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(eager, out)
+
+
+def test_walinear_module_and_host_buffer_entry_point():
+    import ctypes
+    import quant
+    from w4a16 import WALinear
+    lin = torch.nn.Linear(256, 128, bias=True).half().cuda()
+    q = WALinear.from_float(lin, {"n_bit": 4, "group_size": 128})
+    assert q.weight.dtype == torch.int32 and tuple(q.weight.shape) == (256, 16)
+    assert tuple(q.zeros_scales.shape) == (2, 256) and tuple(q.bias.shape) == (1, 128)
+    x = torch.randn(2, 3, 256, dtype=torch.float16, device="cuda")
+    y = q(x)
+    wd = quant.dequant(q.weight, q.zeros_scales, 128, 256, 128)
+    ref = (x.float() @ wd.float().t()).half() + lin.bias.data.half()
+    assert torch.allclose(y.float(), ref.float(), atol=2e-2, rtol=2e-2)
+    # state-dict round trip with the reference's buffer names
+    sd = q.state_dict()
+    assert set(sd) == {"zeros_scales", "weight", "bias"}
+    q2 = WALinear(256, 128, w_bit=4, group_size=128, bias=True)
+    q2.load_state_dict(sd)
+    assert torch.equal(q2(x), y)
+    # host-buffer C-ABI call
+    lib = quant.load_library()
+    M = 6
+    xh = x.reshape(M, 256).cpu().pin_memory()
+    oh = torch.empty(M, 128, dtype=torch.float16).pin_memory()
+    xd = torch.empty(M, 256, dtype=torch.float16, device="cuda")
+    od = torch.empty(M, 128, dtype=torch.float16, device="cuda")
+    st = lib.w4a16_gemm_host(xh.data_ptr(), oh.data_ptr(), xd.data_ptr(), od.data_ptr(), q.weight.data_ptr(),
+                             q.zeros_scales.data_ptr(), q.bias.data_ptr(), M, 128, 256, 128, None, 0,
+                             torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert torch.equal(oh, y.reshape(M, 128).cpu())

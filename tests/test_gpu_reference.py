@@ -1,0 +1,86 @@
+"""Same-box comparison with the reference's own CUDA extension (rebuilt unmodified for sm_100a by
+oracle/build_ref.py).  Skipped when that module was not built."""
+import glob
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import check_gemm_tolerance, make_weight, make_x
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def refq():
+    so = glob.glob(os.path.join(ROOT, "oracle", "_ref", "quant*.so"))
+    if not so:
+        pytest.skip("reference extension not built (oracle/build_ref.py)")
+    spec = importlib.util.spec_from_file_location("quant", so[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def ref_pack(refq, w, K, N, g):
+    import oracle
+    qw8, zeros, scales, _ = oracle.generate_quant(w, 4, g)
+    zs = torch.empty((K // g, 2 * N), dtype=torch.float16, device="cuda")
+    refq.transpose_merge_zeros_scales(zeros.cuda(), scales.cuda(), zs, K, N, g)
+    awq = torch.empty((K, N // 2), dtype=torch.uint8, device="cuda")
+    refq.convert_ours_to_awq(qw8.cuda(), awq, K, N)
+    lmd = torch.empty((K, N // 8), dtype=torch.int32, device="cuda")
+    refq.convert_awq_to_lmdeploy(awq, lmd, K, N)
+    torch.cuda.synchronize()
+    return qw8, zeros, scales, zs, awq, lmd
+
+
+@pytest.mark.parametrize("N,K,g", [(128, 256, 128), (256, 512, 128), (96, 256, 64), (1024, 1024, 128)])
+def test_layout_kernels_byte_identical_to_reference(refq, N, K, g):
+    import quant
+    w = make_weight(N, K, seed=N)
+    qw8, zeros, scales, r_zs, r_awq, r_lmd = ref_pack(refq, w, K, N, g)
+    zs = torch.empty_like(r_zs)
+    quant.transpose_merge_zeros_scales(zeros.cuda(), scales.cuda(), zs, K, N, g)
+    awq = torch.empty_like(r_awq)
+    quant.convert_ours_to_awq(qw8.cuda(), awq, K, N)
+    lmd = torch.empty_like(r_lmd)
+    quant.convert_awq_to_lmdeploy(awq, lmd, K, N)
+    assert torch.equal(zs.view(torch.int16), r_zs.view(torch.int16))
+    assert torch.equal(awq, r_awq)
+    assert torch.equal(lmd, r_lmd)
+
+
+@pytest.mark.parametrize("N,K", [(128, 256), (256, 512), (1024, 1024)])
+def test_dequant_identical_to_reference_kernel_identity_trick(refq, N, K):
+    import quant
+    g = 128
+    w = make_weight(N, K, seed=N + 1)
+    _, _, _, zs, _, lmd = ref_pack(refq, w, K, N, g)
+    eye = torch.eye(K, dtype=torch.float16, device="cuda").unsqueeze(0)
+    ref = refq.gemm_awq_ut(eye, lmd, zs, K, N, K, g)
+    torch.cuda.synchronize()
+    mine = quant.dequant(lmd, zs, N, K, g)
+    a = ref[0].t().contiguous().view(torch.int16).cpu().numpy().view(np.uint16).copy()
+    b = mine.view(torch.int16).cpu().numpy().view(np.uint16).copy()
+    a[(a & 0x7FFF) == 0] = 0
+    b[(b & 0x7FFF) == 0] = 0
+    assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 1024)])
+@pytest.mark.parametrize("M", [1, 8, 16, 64, 512])
+def test_gemm_matches_reference_kernel(refq, N, K, M):
+    import quant
+    g = 128
+    w = make_weight(N, K, seed=N + 2)
+    _, _, _, zs, _, lmd = ref_pack(refq, w, K, N, g)
+    x = make_x(M, K).cuda()
+    ref = refq.gemm_awq_ut(x, lmd, zs, M, N, K, g)
+    torch.cuda.synchronize()
+    mine = quant.gemm_awq_ut(x, lmd, zs, M, N, K, g)
+    wd = quant.dequant(lmd, zs, N, K, g)
+    check_gemm_tolerance(mine[0], ref[0], x, wd.cpu().numpy(), K)
