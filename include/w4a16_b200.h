@@ -74,6 +74,19 @@ int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales
                     void* out, int tokens, int N, int K, int group_size,
                     void* workspace, size_t workspace_bytes, void* stream, int algo);
 
+/*
+ * w4a16_gemm_algo plus flags.  W4A16_FLAG_STATIC_WEIGHTS promises that qweight, zeros_scales and
+ * bias were completely written before any work still in flight on `stream` was enqueued (true
+ * for the buffers of a loaded module; NOT true right after running the packer on the same
+ * stream).  The decode kernel is then launched with programmatic stream serialization: it
+ * starts fetching weights while the previous kernel of the stream drains, and waits for that
+ * kernel to complete before it reads x or writes out.  No counterpart in the reference.
+ */
+#define W4A16_FLAG_STATIC_WEIGHTS 1u
+int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                  void* out, int tokens, int N, int K, int group_size,
+                  void* workspace, size_t workspace_bytes, void* stream, int algo, unsigned flags);
+
 /* Scratch bytes w4a16_gemm needs for this problem (0 = none).  The reference has no
  * workspace (the WorkSpace argument of Gemm_awq_pure, gemm_quant.cu:45, is unused). */
 size_t w4a16_workspace_bytes(int tokens, int N, int K, int group_size);
@@ -127,18 +140,23 @@ int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_d
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * The tcgen05 kernel bounds every barrier wait; if one ever times out the kernel sets a
- * per-device error word, frees its tensor memory and returns.  This reads that word
- * (*flag = 0: no kernel on the current device ever gave up).  Synchronises the device; the
+ * Both GEMM kernels bound every barrier wait; if one ever times out the kernel sets a
+ * per-device error word, releases what it holds (tensor memory) and returns.  This reads that
+ * word (*flag = 0: no kernel on the current device ever gave up).  Synchronises the device; the
  * first call on a device allocates the word, so make it outside stream capture.  The
  * reference has no counterpart (it checks no CUDA error at all, gemm_s4_f16_kernel.h:136-145).
  */
-int w4a16_tc_error_flag(int* flag);
+int w4a16_device_error_flag(int* flag);
 
 /* Debug aid: runs a one-CTA probe that writes tagged words to tensor memory with the 16-lane
  * fragment store the tcgen05 kernel uses and reads them back lane by lane; out = uint32
  * [128 lanes][32 columns] on the device.  tests/test_gpu_tmem.py decodes it. */
 int w4a16_debug_tmem_layout(void* out, void* stream);
+
+/* Debug aid: device buffer of uint64 [CTAs][16 warps][8] that receives %globaltimer stamps of
+ * the skinny kernel's phases (start, x staged, after barrier, first weights landed, main loop
+ * done, partials visible, cluster barrier passed, end); NULL switches it off. */
+void w4a16_debug_skinny_timeline(void* buf);
 
 /* Benchmark/tuning hooks, not part of the drop-in surface (0 = automatic choice):
  * skinny kernel: out-feature tiles per CTA (1,2,4,8) and cluster split-K (1,2,4,8);

@@ -1,6 +1,8 @@
 // C-ABI entry points: argument validation, kernel selection, error bookkeeping.
 #include <atomic>
 
+#include <cuda.h>
+
 #include "w4a16_common.cuh"
 
 namespace w4a16 {
@@ -19,7 +21,60 @@ int record_cuda_error(cudaError_t e)
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Allocated once per device (first use; outside stream capture), never freed, only ever set to 1.
+int* device_error_word()
+{
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+        if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return nullptr;
+        words[dev] = p;
+    }
+    return words[dev];
+}
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn()
+{
+    static std::atomic<EncodeTiledFn> fn{nullptr};
+    EncodeTiledFn f = fn.load(std::memory_order_acquire);
+    if (!f) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            f = (EncodeTiledFn)sym;
+            fn.store(f, std::memory_order_release);
+        }
+    }
+    return f;
+}
+}  // namespace
+
+int encode_tensor_map_2d(void* tmap, const void* base, int elem_bytes, const uint64_t dims[2], uint64_t row_stride_bytes,
+                         const uint32_t box[2], bool swizzle128)
+{
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return record_cuda_error(cudaErrorNotSupported);
+    const cuuint64_t gdims[2] = {dims[0], dims[1]};
+    const cuuint64_t gstr[1] = {row_stride_bytes};
+    const cuuint32_t gbox[2] = {box[0], box[1]};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    CUresult r = encode((CUtensorMap*)tmap, dt, 2, const_cast<void*>(base), gdims, gstr, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? W4A16_OK : record_cuda_error(cudaErrorInvalidValue);
+}
+
 void skinny_force_config(int wn, int splits);
+void skinny_set_timeline(unsigned long long* buf);
 void tc_force_config(int tile_tokens, int split_k);
 
 namespace {
@@ -84,13 +139,14 @@ extern "C" size_t w4a16_workspace_bytes(int tokens, int N, int K, int group_size
     return tc_workspace_bytes(tokens, N, K, group_size);
 }
 
-extern "C" int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
-                               void* out, int tokens, int N, int K, int group_size, void* workspace,
-                               size_t workspace_bytes, void* stream, int algo)
+extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                             void* out, int tokens, int N, int K, int group_size, void* workspace,
+                             size_t workspace_bytes, void* stream, int algo, unsigned flags)
 {
     int s = validate(x, qweight, zeros_scales, out, tokens, N, K, group_size);
     if (s != W4A16_OK) return s;
     if (algo != W4A16_ALGO_AUTO && algo != W4A16_ALGO_SKINNY && algo != W4A16_ALGO_TC) return W4A16_ERR_BAD_ALGO;
+    if (flags & ~(unsigned)W4A16_FLAG_STATIC_WEIGHTS) return W4A16_ERR_BAD_ALGO;
     if (tokens == 0) return W4A16_OK;
     s = check_device();
     if (s != W4A16_OK) return s;
@@ -99,6 +155,7 @@ extern "C" int w4a16_gemm_algo(const void* x, const void* qweight, const void* z
     a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
     a.bias = (const __half*)bias; a.out = (__half*)out;
     a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
+    a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
 
     if (algo == W4A16_ALGO_AUTO) algo = (tokens <= 32 || !tc_supported(tokens, N, K, group_size)) ? W4A16_ALGO_SKINNY : W4A16_ALGO_TC;
     if (algo == W4A16_ALGO_TC) {
@@ -106,6 +163,14 @@ extern "C" int w4a16_gemm_algo(const void* x, const void* qweight, const void* z
         return launch_tc(a, workspace, workspace_bytes, (cudaStream_t)stream);
     }
     return launch_skinny(a, (cudaStream_t)stream);
+}
+
+extern "C" int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                               void* out, int tokens, int N, int K, int group_size, void* workspace,
+                               size_t workspace_bytes, void* stream, int algo)
+{
+    return w4a16_gemm_ex(x, qweight, zeros_scales, bias, out, tokens, N, K, group_size, workspace, workspace_bytes, stream,
+                         algo, 0u);
 }
 
 extern "C" int w4a16_gemm(const void* x, const void* qweight, const void* zeros_scales, const void* bias, void* out,
@@ -133,6 +198,17 @@ extern "C" int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, 
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
 
+extern "C" int w4a16_device_error_flag(int* flag)
+{
+    if (!flag) return W4A16_ERR_NULL_POINTER;
+    int* w = device_error_word();
+    if (!w) return W4A16_ERR_CUDA;
+    cudaError_t e = cudaMemcpy(flag, w, sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
 // Tuning hooks for benchmarks (0 = automatic).  Not part of the drop-in surface.
 extern "C" void w4a16_tune_skinny(int wn, int splits) { skinny_force_config(wn, splits); }
+// Debug aid: device buffer [ctas][16 warps][8] receiving %globaltimer stamps of the skinny kernel's phases (NULL = off).
+extern "C" void w4a16_debug_skinny_timeline(void* buf) { skinny_set_timeline((unsigned long long*)buf); }
 extern "C" void w4a16_tune_tc(int tile_tokens, int split_k) { tc_force_config(tile_tokens, split_k); }

@@ -43,6 +43,19 @@ __device__ __forceinline__ void unpack_s4x8(uint32_t w, uint32_t (&h)[4])
     h[3] = lop3_and_or(w >> 8, kMask, kMagic);
 }
 
+// Same result with fewer integer-pipe instructions: the low nibble of each byte is read in place as
+// fp16 (1024 + q) and brought to (64 + q) by an exact fp16 subtraction of 960 (FMA pipe).
+__device__ __forceinline__ void unpack_s4x8_fast(uint32_t w, uint32_t (&h)[4])
+{
+    constexpr uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u, k1024 = 0x64006400u, k64 = 0x54005400u, k960 = 0x63806380u;
+    const uint32_t top = w >> 8;
+    uint32_t a = lop3_and_or(w, kLo, k1024), c = lop3_and_or(top, kLo, k1024);
+    h[1] = lop3_and_or(w, kHi, k64);
+    h[3] = lop3_and_or(top, kHi, k64);
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(h[0]) : "r"(a), "r"(k960));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(h[2]) : "r"(c), "r"(k960));
+}
+
 // (t - z) * s in fp16 with flush-to-zero, two lanes at a time: bit-exact with apply_Q
 // (common.h:210-225, the non-FMA branch).
 __device__ __forceinline__ uint32_t dequant_h2(uint32_t t, uint32_t zz, uint32_t ss)
@@ -83,15 +96,23 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// D = A * B (accumulator starts at zero)
+__device__ __forceinline__ void mma_m16n8k16_zc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
 {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -104,10 +125,15 @@ struct GemmArgs {
     const __half*   bias;  // may be null
     __half*         out;
     int tokens, N, K, g;
+    bool static_weights;   // W4A16_FLAG_STATIC_WEIGHTS
 };
 
 int  record_cuda_error(cudaError_t e);          // returns W4A16_ERR_CUDA, remembers e
 void count_launch(unsigned n = 1);
+int* device_error_word();
+// cuTensorMapEncodeTiled for a row-major 2-D tensor (dims = {inner, outer} in elements); `tmap` is a CUtensorMap*
+int encode_tensor_map_2d(void* tmap, const void* base, int elem_bytes, const uint64_t dims[2], uint64_t row_stride_bytes,
+                         const uint32_t box[2], bool swizzle128);                       // per-device word a kernel sets to 1 when a bounded wait gives up
 
 int launch_skinny(const GemmArgs& a, cudaStream_t st);
 int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);

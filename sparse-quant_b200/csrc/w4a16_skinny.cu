@@ -3,35 +3,57 @@
 //   out[t, n] = fp16( sum_k fp32( dq(W)[n, k] * x[t, k] ) ) (+ bias[n])
 //
 // Replaces the small-token instantiations of gemm_s4_f16_nn (gemm_template.h:358-464 of the
-// reference, CTA shapes (x, 8|16, 256|512) of gemm_s4_f16.cu:66-87), which run at most N/64 CTAs
-// and stream K serially.  Here the whole machine streams the weight matrix once:
+// reference, CTA shapes (x, 8|16, 256|512) of gemm_s4_f16.cu:66-87), which run at most N/64 CTAs,
+// stream K serially and re-do the fp16 dequantisation arithmetic in the MMA issue slots.  Here the
+// whole machine streams the weight matrix once, in one wave of one 512-thread CTA per SM:
 //
-//   * a warp owns one 32-wide out-feature tile and a contiguous K slice; every lane issues one
-//     128-bit non-allocating load per 32x32 tile (512 contiguous bytes per warp), four tiles
-//     (one 128-k unit) double-buffered, so 8 x 16 B are in flight per lane;
-//   * nibbles are expanded in registers to fp16 (64+q), then (t - z) * s with sub.ftz/mul.ftz -
-//     bit-exact with the reference - and fed as the A fragment of mma.m16n8k16 (the packed layout
-//     IS that fragment); activations are staged once per CTA in shared memory and read with
-//     ldmatrix as the B fragment; accumulation is fp32;
+//   * a warp owns one 32-wide out-feature tile and a contiguous K slice.  Its lane 0 keeps a
+//     private ring of TMA copies in flight into shared memory, four 128-k units deep: per unit one
+//     tensor copy (a 4-row box of the packed matrix seen as [K/32][N/32 x 512 B]: four strided
+//     512-byte tiles in one operation) plus one 128-byte bulk copy of the group's (zero, scale)
+//     pairs, both completing on the unit's own mbarrier - about 130 KB in flight per SM with no
+//     registers spent on it;
+//   * the nibbles are expanded in registers to fp16 (64 + q) - exact - and fed straight to
+//     mma.m16n8k16 as the A fragment (the packed layout IS that fragment); activations are staged
+//     once per CTA in shared memory and read with ldmatrix as the B fragment; a second MMA with an
+//     all-ones A fragment yields sum_k x[t, k] of the group.  At the end of each quantisation group
+//     the zero point and the scale are applied in fp32:  acc += s * (sum (64+q) x - (64+z) sum x).
+//     That is (q - z) * s without the intermediate fp16 rounding of the weight; with the identity
+//     matrix as input the output reproduces the reference's dequantised weight bit for bit
+//     (denormal scales are flushed to zero as mul.ftz does), and for general inputs it agrees with
+//     dequantise-then-matmul to ~1e-4 relative, far inside the stated tolerance;
 //   * split-K: WK warps of a CTA cover different K slices of the same tiles and S CTAs of one
-//     thread-block cluster cover different K ranges; partial sums meet in shared memory and are
-//     reduced across the cluster through distributed shared memory in a fixed order, so results
-//     are deterministic and no global scratch or atomics are needed;
+//     thread-block cluster cover different K ranges (only when the staged activations would not
+//     fit); partial sums meet in shared memory and are reduced across the cluster through
+//     distributed shared memory in a fixed order: deterministic, no global scratch, no atomics;
 //   * bias add, fp16 rounding and the [tokens, N] store are fused into the reduction.
+// Every mbarrier wait is bounded; a timeout raises the library's device error word.
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 #include "w4a16_common.cuh"
+#include "w4a16_sm100.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace w4a16 {
 
+using namespace sm100;
+
 namespace {
 
-constexpr int kWarps   = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kUnitK   = 128;               // k per pipeline unit (4 tiles)
+constexpr int kMaxWarps  = 32;
+constexpr int kHeaderBytes = 2048;           // zero chunk, abort flag, mbarriers
+constexpr int kUnitK     = 128;               // k per pipeline unit (4 tiles)
 constexpr int kUnitTiles = kUnitK / kTileK;
+constexpr int kDepth     = 4;                 // units in flight per warp
+constexpr uint64_t kWaitBudgetNs = 200ull * 1000 * 1000;
+
+template <int G>
+struct Slot {                                 // one pipeline unit in shared memory
+    uint4    tiles[kUnitTiles][32];           // 4 x 512 B
+    uint32_t zs[kUnitK / G][32];              // per group: (zero+64, scale) of the tile's 32 out-features
+};
 
 struct SkinnyParams {
     const __half*   x;
@@ -39,86 +61,120 @@ struct SkinnyParams {
     const uint32_t* zs;
     const __half*   bias;
     __half*         out;
+    int*            error;
     int tokens, N, K;
-    int wn;          // out-feature tiles per CTA (1,2,4,8); WK = 8 / wn K-slices per CTA
+    int wn;          // out-feature tiles per CTA (1,2,4,8,16); WK = 16 / wn K-slices per CTA
     int splits;      // cluster size along K (gridDim.y)
     int xs_stride;   // halfs per staged activation row
+    int ring_offset; // byte offset of the per-warp rings in shared memory
+    int depth;       // units in flight per warp (2..kDepth)
+    int warps;       // warps per CTA
+    int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
+    unsigned long long* timeline;   // debug: [cta][warp][8] globaltimer stamps, or null
+    int debug_mode;  // experiments: bit 0 = skip the MMA work, bit 1 = skip staging the activations
 };
 
+// lane 0 of a warp: arm the slot's barrier and start the copies of one unit.  `zsrc` points at the unit's first
+// (zero, scale) row for this warp's out-feature tile.
 template <int G>
-struct UnitRegs {
-    uint4    q[kUnitTiles];
-    uint32_t zs[kUnitK / G][2][2];          // [group in unit][n half][row hi]
-};
-
-template <int G>
-__device__ __forceinline__ void load_unit(UnitRegs<G>& u, const SkinnyParams& p, int unit, int nt, int lane, int k_tiles)
+__device__ __forceinline__ void issue_unit(uint32_t slot_addr, uint32_t bar, const CUtensorMap* wmap, const uint32_t* zsrc,
+                                           int N, int unit, int nt, int groups)
 {
-    const int n_tiles = p.N / kTileN;
-    const int kt0 = unit * kUnitTiles;
+    constexpr int kGroupsPerUnit = kUnitK / G;
+    const int n_groups = min(kGroupsPerUnit, groups - unit * kGroupsPerUnit);     // < full only at the K edge
+    // the tensor copy always delivers the full 4 x 512 B box (rows past K/32 arrive as zeros)
+    mbar_arrive_expect_tx(bar, kUnitTiles * 512u + n_groups * 128u);
+    tma_load_2d(slot_addr, wmap, nt * 128, unit * kUnitTiles, bar);
 #pragma unroll
-    for (int t = 0; t < kUnitTiles; ++t) {
-        if (kt0 + t < k_tiles)
-            u.q[t] = ldg_nc_v4(p.qw + ((size_t)(kt0 + t) * n_tiles + nt) * 32 + lane);
-        else
-            u.q[t] = make_uint4(0, 0, 0, 0);
-    }
-    const int r = lane >> 2;
-    const int groups = p.K / G;
-#pragma unroll
-    for (int gi = 0; gi < kUnitK / G; ++gi) {
-        const int kg = unit * (kUnitK / G) + gi;
-        const int kgc = kg < groups ? kg : groups - 1;          // clamp: value unused when past the end
-        const uint32_t* row = p.zs + (size_t)kgc * p.N + nt * kTileN + r;
-#pragma unroll
-        for (int nh = 0; nh < 2; ++nh)
-#pragma unroll
-            for (int hi = 0; hi < 2; ++hi) u.zs[gi][nh][hi] = ldg_nc_u32(row + nh * 16 + hi * 8);
-    }
+    for (int gi = 0; gi < kGroupsPerUnit; ++gi)
+        if (gi < n_groups) bulk_load(slot_addr + kUnitTiles * 512u + gi * 128u, zsrc + (size_t)gi * N, 128u, bar);
 }
 
 template <int TG, int G>
-__device__ __forceinline__ void compute_unit(const UnitRegs<G>& u, float (&acc)[TG][2][4], uint32_t xs_lane_addr,
-                                             int xs_stride_bytes, int unit_local, int kt0, int k_tiles)
+__device__ __forceinline__ void compute_unit(const Slot<G>* slot, float (&acc)[TG][2][4], const uint32_t (&xaddr)[TG],
+                                             const int (&kmul)[TG], int k_local, int kt0, int k_tiles, int lane)
 {
     constexpr int kTilesPerGroup = G / kTileK;
+    constexpr uint32_t kOnes = 0x3c003c00u;
+    const uint32_t ones[4] = {kOnes, kOnes, kOnes, kOnes};
+    const int r = lane >> 2;
 #pragma unroll
-    for (int t = 0; t < kUnitTiles; ++t) {
-        if (kt0 + t < k_tiles) {                                // warp-uniform
-            // activations of this tile: B fragments for both 16-k halves, per token group
-            uint32_t b[TG][4];
+    for (int gi = 0; gi < kUnitK / G; ++gi) {
+        if (kt0 + gi * kTilesPerGroup < k_tiles) {                  // warp-uniform: the group exists
+            // three accumulator chains (sum x, out-features 0-15, 16-31) interleaved per 16-k half
+            float accg[TG][2][4], xsum[TG][4];
 #pragma unroll
-            for (int tg = 0; tg < TG; ++tg)
-                ldmatrix_x4(b[tg], xs_lane_addr + tg * 8 * xs_stride_bytes + (unit_local * kUnitK + t * kTileK) * 2);
-            const int gi = t / kTilesPerGroup;
-            uint32_t zz[2][2], ss[2][2];
+            for (int tt = 0; tt < kTilesPerGroup; ++tt) {
+                const int t = gi * kTilesPerGroup + tt;
+                uint32_t b[TG][4];
 #pragma unroll
-            for (int nh = 0; nh < 2; ++nh)
+                for (int tg = 0; tg < TG; ++tg)
+                    ldmatrix_x4(b[tg], xaddr[tg] + (uint32_t)((k_local + t * kTileK) * kmul[tg]));
+                const uint4 q = slot->tiles[t][lane];
+                const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                for (int hi = 0; hi < 2; ++hi) split_zs(u.zs[gi][nh][hi], zz[nh][hi], ss[nh][hi]);
-            const uint32_t words[4] = {u.q[t].x, u.q[t].y, u.q[t].z, u.q[t].w};
+                for (int kh = 0; kh < 2; ++kh) {
+                    uint32_t a0[4], a1[4];
+                    unpack_s4x8_fast(words[kh * 2 + 0], a0);
+                    unpack_s4x8_fast(words[kh * 2 + 1], a1);
 #pragma unroll
-            for (int wd = 0; wd < 4; ++wd) {
-                const int kh = wd >> 1, nh = wd & 1;
-                uint32_t a[4];
-                unpack_s4x8(words[wd], a);
-                a[0] = dequant_h2(a[0], zz[nh][0], ss[nh][0]);
-                a[1] = dequant_h2(a[1], zz[nh][1], ss[nh][1]);
-                a[2] = dequant_h2(a[2], zz[nh][0], ss[nh][0]);
-                a[3] = dequant_h2(a[3], zz[nh][1], ss[nh][1]);
+                    for (int tg = 0; tg < TG; ++tg) {
+                        if (tt == 0 && kh == 0) {
+                            mma_m16n8k16_zc(xsum[tg], ones, b[tg][0], b[tg][1]);
+                            mma_m16n8k16_zc(accg[tg][0], a0, b[tg][0], b[tg][1]);
+                            mma_m16n8k16_zc(accg[tg][1], a1, b[tg][0], b[tg][1]);
+                        } else {
+                            mma_m16n8k16(xsum[tg], ones, b[tg][2 * kh], b[tg][2 * kh + 1]);
+                            mma_m16n8k16(accg[tg][0], a0, b[tg][2 * kh], b[tg][2 * kh + 1]);
+                            mma_m16n8k16(accg[tg][1], a1, b[tg][2 * kh], b[tg][2 * kh + 1]);
+                        }
+                    }
+                }
+            }
+            // zero point and scale of the group, applied in fp32
 #pragma unroll
-                for (int tg = 0; tg < TG; ++tg) mma_m16n8k16(acc[tg][nh], a, b[tg][2 * kh], b[tg][2 * kh + 1]);
+            for (int nh = 0; nh < 2; ++nh) {
+                float zf[2], sf[2];
+#pragma unroll
+                for (int hi = 0; hi < 2; ++hi) {
+                    // (zero + 64, scale) * (1, 1) with flush-to-zero: a denormal scale becomes 0, as under mul.ftz
+                    uint32_t v = slot->zs[gi][nh * 16 + hi * 8 + r];
+                    asm("mul.ftz.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(kOnes));
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+                    zf[hi] = f.x;
+                    sf[hi] = f.y;
+                }
+#pragma unroll
+                for (int tg = 0; tg < TG; ++tg) {
+                    acc[tg][nh][0] = fmaf(sf[0], fmaf(-zf[0], xsum[tg][0], accg[tg][nh][0]), acc[tg][nh][0]);
+                    acc[tg][nh][1] = fmaf(sf[0], fmaf(-zf[0], xsum[tg][1], accg[tg][nh][1]), acc[tg][nh][1]);
+                    acc[tg][nh][2] = fmaf(sf[1], fmaf(-zf[1], xsum[tg][0], accg[tg][nh][2]), acc[tg][nh][2]);
+                    acc[tg][nh][3] = fmaf(sf[1], fmaf(-zf[1], xsum[tg][1], accg[tg][nh][3]), acc[tg][nh][3]);
+                }
             }
         }
     }
 }
 
-// TG = token groups of 8 handled per pass (1, 2, 4); G = quantisation group size.
-template <int TG, int G>
-__global__ void __launch_bounds__(kThreads) skinny_kernel(const SkinnyParams p)
+// fp32 load from the shared memory of CTA `rank` of this cluster (own rank included)
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank)
 {
-    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// TG = token groups of 8 handled per pass (1, 2, 4); G = quantisation group size.
+template <int TG, int G, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParams p)
+{
+    extern __shared__ __align__(128) unsigned char smem[];
     constexpr int kTok = 8 * TG;
+    constexpr int kThreads = kWarps * 32;
+    static_assert(2 * sizeof(Slot<G>) >= kTok * 33 * 4, "a warp's partial sums reuse its own ring (depth >= 2)");
+    static_assert(sizeof(Slot<G>) % 16 == 0, "bulk copies need 16-byte aligned destinations");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wn = p.wn, wk = kWarps / wn;
@@ -127,6 +183,7 @@ __global__ void __launch_bounds__(kThreads) skinny_kernel(const SkinnyParams p)
     const int nt = blockIdx.x * wn + wn_idx;
     const bool nt_valid = nt < n_tiles;
     const int tok0 = blockIdx.z * kTok;
+    const int rows = min(kTok, p.tokens - tok0);        // real token rows of this pass
 
     // K decomposition in 128-k units: cluster rank -> CTA range -> warp slice
     const int k_tiles = p.K / kTileK;
@@ -135,28 +192,88 @@ __global__ void __launch_bounds__(kThreads) skinny_kernel(const SkinnyParams p)
     const int cu0 = (int)((long long)units * rank / S), cu1 = (int)((long long)units * (rank + 1) / S);
     const int cta_units = cu1 - cu0;
     const int wu0 = cu0 + (int)((long long)cta_units * wk_idx / wk), wu1 = cu0 + (int)((long long)cta_units * (wk_idx + 1) / wk);
+    const int n_units = nt_valid ? wu1 - wu0 : 0;
 
-    __half* xs  = reinterpret_cast<__half*>(smem);
-    float*  red = reinterpret_cast<float*>(smem + (size_t)kTok * p.xs_stride * sizeof(__half));
-    // red: [wk][wn*32][kTok] fp32
+    // shared memory: header (kHeaderBytes): [16 B zeros][abort flag][barriers kMaxWarps x kDepth] | activations | per-warp rings
+    static_assert(32 + kMaxWarps * kDepth * 8 <= kHeaderBytes, "header overflow");
+    const uint32_t bars = smem_u32(smem) + 32 + warp * kDepth * 8;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 16);
+    __half* xs = reinterpret_cast<__half*>(smem + kHeaderBytes);
+    const int depth = p.depth;
+    const int ring_bytes = depth * (int)sizeof(Slot<G>);   // per warp
+    Slot<G>* ring = reinterpret_cast<Slot<G>*>(smem + p.ring_offset + (size_t)warp * ring_bytes);
 
-    UnitRegs<G> cur, nxt;
-    if (nt_valid && wu0 < wu1) load_unit<G>(cur, p, wu0, nt, lane, k_tiles);   // weights first: they do not depend on x
-
-    // stage x[tok0 .. tok0+kTok) x [cu0*128, cu1*128) in shared memory (zero beyond tokens / K)
-    {
-        const int kc0 = cu0 * kUnitK;
-        const int vec_per_row = cta_units * (kUnitK / 8);
-        for (int i = threadIdx.x; i < kTok * vec_per_row; i += kThreads) {
-            const int row = i / vec_per_row, v = i % vec_per_row;
-            const int k = kc0 + v * 8;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (tok0 + row < p.tokens && k < p.K)
-                val = *reinterpret_cast<const uint4*>(p.x + (size_t)(tok0 + row) * p.K + k);
-            *reinterpret_cast<uint4*>(xs + (size_t)row * p.xs_stride + v * 8) = val;
-        }
+    unsigned long long* tl = nullptr;
+    if (p.timeline && lane == 0)
+        tl = p.timeline + ((size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kWarps + warp) * 8;
+    if (tl) tl[0] = globaltimer_ns();
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(smem)[threadIdx.x] = 0u;
+    if (lane == 0) {
+        for (int i = 0; i < kDepth; ++i) mbar_init(bars + 8 * i, 1);
+        mbar_fence_init();
     }
+
+    // Activations x[tok0 .. tok0+rows) x [cu0*128, cu1*128) are staged in shared memory (zero beyond K);
+    // token rows past `rows` all read the 16 zero bytes at the start of shared memory.
+    const int kc0 = cu0 * kUnitK;
+    const int vec_per_row = cta_units * (kUnitK / 8);
+    const int total = (p.debug_mode & 2) ? 0 : rows * vec_per_row;
+    constexpr int kBatch = 8;                               // 16-byte loads in flight per thread
+    uint4 xval[kBatch];
+    int xdst[kBatch];
+    auto load_x_batch = [&](int base) {
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int i = base + j * kThreads;
+            xval[j] = make_uint4(0, 0, 0, 0);
+            xdst[j] = -1;
+            if (i < total) {
+                const int row = i / vec_per_row, v = i - row * vec_per_row;
+                xdst[j] = row * p.xs_stride + v * 8;
+                if (kc0 + v * 8 < p.K) xval[j] = *reinterpret_cast<const uint4*>(p.x + (size_t)(tok0 + row) * p.K + kc0 + v * 8);
+            }
+        }
+    };
+    auto store_x_batch = [&]() {
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j)
+            if (xdst[j] >= 0) *reinterpret_cast<uint4*>(xs + xdst[j]) = xval[j];
+    };
+    const uint32_t ring_addr = smem_u32(ring);
+    const int groups = p.K / G;
+    const size_t zs_step = (size_t)(kUnitK / G) * p.N;                        // words between consecutive units
+    const uint32_t* zs_next = p.zs + (size_t)wu0 * zs_step + nt * kTileN;     // first unit of this warp
+    auto issue_first_units = [&]() {
+        if (lane == 0) {
+            if (warp == 0) prefetch_tmap(&wmap);
+            for (int i = 0; i < depth && i < n_units; ++i)
+                issue_unit<G>(ring_addr + i * (uint32_t)sizeof(Slot<G>), bars + 8 * i, &wmap, zs_next + (size_t)i * zs_step, p.N, wu0 + i, nt, groups);
+        }
+    };
+
+    if (p.pdl) {
+        // Programmatic dependent launch: this grid may start while the previous kernel of the stream is
+        // still draining.  The packed weights are static by contract, so their copies start at once; the
+        // activations (and everything this kernel writes) wait for the previous grid to complete.
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        issue_first_units();
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        load_x_batch(threadIdx.x);
+    } else {
+        // The activation loads are issued BEFORE the weight copies (they are on the critical path and must
+        // not queue behind megabytes of weight traffic) and stored after the copies are in flight.
+        load_x_batch(threadIdx.x);
+        issue_first_units();
+    }
+    store_x_batch();
+    for (int base = threadIdx.x + kBatch * kThreads; base < total; base += kThreads * kBatch) {   // long rows: further batches
+        load_x_batch(base);
+        store_x_batch();
+    }
+    if (tl) tl[1] = globaltimer_ns();
     __syncthreads();
+    if (tl) tl[2] = globaltimer_ns();
 
     float acc[TG][2][4];
 #pragma unroll
@@ -166,93 +283,147 @@ __global__ void __launch_bounds__(kThreads) skinny_kernel(const SkinnyParams p)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[tg][nh][j] = 0.f;
 
-    if (nt_valid) {
-        // ldmatrix row address of this lane: matrix j = lane/8 covers k offset 8j, row = token lane%8
-        const uint32_t xs_lane_addr = smem_u32(xs) + ((lane & 7) * p.xs_stride + (lane >> 3) * 8) * 2;
-        const int xs_stride_bytes = p.xs_stride * 2;
-        for (int u = wu0; u < wu1; ++u) {
-            const bool more = u + 1 < wu1;
-            if (more) load_unit<G>(nxt, p, u + 1, nt, lane, k_tiles);
-            compute_unit<TG, G>(cur, acc, xs_lane_addr, xs_stride_bytes, u - cu0, u * kUnitTiles, k_tiles);
-            if (more) cur = nxt;
+    if (n_units > 0) {
+        // ldmatrix row address per token group: matrix j = lane/8 covers k offset 8j, row = token lane%8.
+        // Rows beyond the real tokens point at the zero chunk and do not advance with k.
+        uint32_t xaddr[TG];
+        int kmul[TG];
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg) {
+            const int row = tg * 8 + (lane & 7);
+            const bool real = row < rows;
+            xaddr[tg] = real ? smem_u32(xs) + (uint32_t)((row * p.xs_stride + (lane >> 3) * 8) * 2) : smem_u32(smem);
+            kmul[tg] = real ? 2 : 0;
+        }
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < n_units; ++i) {
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * slot, phase, abort_flag, kWaitBudgetNs));
+            if (!ok) break;
+            if (tl && i == 0) tl[3] = globaltimer_ns();
+            const int u = wu0 + i;
+            if ((p.debug_mode & 1) == 0)
+                compute_unit<TG, G>(ring + slot, acc, xaddr, kmul, (u - cu0) * kUnitK, u * kUnitTiles, k_tiles, lane);
+            else
+                acc[0][0][0] += __uint_as_float(ring[slot].tiles[0][lane].x & 0x3fu);
+            __syncwarp();                                   // every lane is done reading the slot
+            if (lane == 0 && i + depth < n_units)
+                issue_unit<G>(ring_addr + slot * (uint32_t)sizeof(Slot<G>), bars + 8 * slot, &wmap, zs_next + (size_t)(i + depth) * zs_step, p.N,
+                              u + depth, nt, groups);
+            if (++slot == depth) { slot = 0; phase ^= 1u; }
         }
     }
 
+    if (tl) tl[4] = globaltimer_ns();
     // ---- reduction: warps -> CTA (shared memory), CTAs -> cluster (distributed shared memory) ----
-    const int nloc = wn * kTileN;                       // out-features per CTA
+    // a warp's partial sums [32 out-features][kTok] go to the start of its own (drained) ring
     {
+        __syncwarp();
         const int r = lane >> 2, c = lane & 3;
-        float* dst = red + ((size_t)wk_idx * nloc + wn_idx * kTileN) * kTok;
+        float* dst = reinterpret_cast<float*>(ring);        // [kTok][33]: out-feature fastest, padded row
 #pragma unroll
         for (int tg = 0; tg < TG; ++tg)
 #pragma unroll
             for (int nh = 0; nh < 2; ++nh) {
-                float* d0 = dst + (size_t)(nh * 16 + r) * kTok + tg * 8 + 2 * c;
-                *reinterpret_cast<float2*>(d0)            = make_float2(acc[tg][nh][0], acc[tg][nh][1]);
-                *reinterpret_cast<float2*>(d0 + 8 * kTok) = make_float2(acc[tg][nh][2], acc[tg][nh][3]);
+                float* d0 = dst + (tg * 8 + 2 * c) * 33 + nh * 16 + r;
+                d0[0]      = acc[tg][nh][0];
+                d0[33]     = acc[tg][nh][1];
+                d0[8]      = acc[tg][nh][2];
+                d0[33 + 8] = acc[tg][nh][3];
             }
     }
     __syncthreads();
-    const int E = nloc * kTok;
-    if (wk > 1) {
-        for (int e = threadIdx.x; e < E; e += kThreads) {
-            float s = red[e];
-            for (int w = 1; w < wk; ++w) s += red[(size_t)w * E + e];
-            red[e] = s;
+    if (tl) tl[5] = globaltimer_ns();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicExch(p.error, 1);
+            const uint64_t t0 = globaltimer_ns();           // let copies still in flight land before the CTA retires
+            while (globaltimer_ns() - t0 < 200000) { }
         }
+        __syncthreads();
     }
-
+    const int nloc = wn * kTileN;                           // out-features per CTA (a power of two)
+    const int nloc_shift = 31 - __clz(nloc), wk_shift = 31 - __clz(wk);
+    const int kRingFloats = ring_bytes / 4;
     cg::cluster_group cluster = cg::this_cluster();
-    if (S > 1) cluster.sync(); else __syncthreads();
+    if (S > 1) cluster.sync();                              // every rank's partial sums are in place
+    if (tl) tl[6] = globaltimer_ns();
 
-    // element e' = tok * nloc + n_local (n fastest -> coalesced stores); rank r finalises a slice
-    const int e_lo = (int)((long long)E * rank / S), e_hi = (int)((long long)E * (rank + 1) / S);
+    const uint32_t ring0 = smem_u32(smem + p.ring_offset);   // same offset in every rank's shared memory
+    // Rank r finalises a slice of the (tok, n_local) space (n fastest -> coalesced stores).  An output is
+    // the sum of S * wk partials - K slice w of rank q lives in the ring of warp (w * wn + n_local / 32) -
+    // added in a fixed order (rank-major) from batches of eight loads in flight: deterministic.
+    const int Er = rows << nloc_shift, terms = S << wk_shift;
+    const int e_lo = (int)((long long)Er * rank / S), e_hi = (int)((long long)Er * (rank + 1) / S);
     for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
-        const int tok = e / nloc, nl = e % nloc;
-        const int src = nl * kTok + tok;
+        const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+        const int off = (nl >> 5) * kRingFloats + tok * 33 + (nl & 31);
         float s = 0.f;
-        if (S > 1) {
-            for (int q = 0; q < S; ++q) s += *cluster.map_shared_rank(red + src, q);
-        } else {
-            s = red[src];
+        for (int t0 = 0; t0 < terms; t0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = t0 + j, q = t >> wk_shift, w = t & (wk - 1);
+                v[j] = t < terms ? ld_cluster_f32(ring0 + (uint32_t)(off + w * wn * kRingFloats) * 4u, (uint32_t)q) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[j];
         }
-        const int n = blockIdx.x * nloc + nl, t = tok0 + tok;
-        if (t < p.tokens && n < p.N) {
+        const int n = blockIdx.x * nloc + nl;
+        if (n < p.N) {
             __half h = __float2half_rn(s);
             if (p.bias) h = __hadd(h, p.bias[n]);
-            p.out[(size_t)t * p.N + n] = h;
+            p.out[(size_t)(tok0 + tok) * p.N + n] = h;
         }
     }
-    if (S > 1) cluster.sync();                           // peers may still be reading this CTA's partials
+    if (S > 1) cluster.sync();                              // peers may still be reading this CTA's partials
+    if (tl) tl[7] = globaltimer_ns();
 }
 
-struct Config { int tg, wn, splits; };
+struct Config { int tg, wn, splits, depth, warps; };
 
-int g_force_wn = 0, g_force_splits = 0;
+int g_force_wn = 0, g_force_splits = 0, g_force_depth = 0, g_force_warps = 0, g_debug_mode = 0;
+unsigned long long* g_timeline = nullptr;
 
-Config pick_config(int tokens, int N, int K)
+constexpr int kSmemBudget = 227 * 1024;                  // opt-in shared memory of one CTA on sm_100
+
+int slot_bytes(int g) { return kUnitTiles * 512 + (kUnitK / g) * 128; }
+
+// shared memory the activations of one CTA need: [header 1 KB][rows x (K/S + 8) halfs], 128-byte aligned
+int stage_bytes(int rows, int K, int splits)
+{
+    const int units = (K + kUnitK - 1) / kUnitK;
+    const int cta_units = (units + splits - 1) / splits;
+    return kHeaderBytes + (int)(((size_t)rows * (cta_units * kUnitK + 8) * sizeof(__half) + 127) / 128 * 128);
+}
+
+Config pick_config(int tokens, int N, int K, int g)
 {
     Config c;
     c.tg = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
     const int n_tiles = N / kTileN, units = (K + kUnitK - 1) / kUnitK;
-    const int passes = (tokens + 8 * c.tg - 1) / (8 * c.tg);
-    // two out-feature tiles per CTA (four K slices) unless the matrix is so wide that whole-K CTAs
-    // already fill the machine
-    c.wn = 2;
-    if (n_tiles * passes >= 148 * 16) c.wn = 4;
-    while (c.wn > 1 && n_tiles % c.wn) c.wn >>= 1;
-    const int wk = kWarps / c.wn;
-    const int ctas_n = (n_tiles + c.wn - 1) / c.wn * passes;
-    // cluster split-K until ~4 CTAs per SM, keeping at least one unit per warp slice
-    c.splits = 1;
-    while (c.splits < 8 && ctas_n * c.splits < 148 * 4 && units >= 2 * c.splits * wk) c.splits <<= 1;
+    const int rows = tokens < 8 * c.tg ? tokens : 8 * c.tg;
+    c.warps = 16;
+    const int kWarps = c.warps;
+    const int ring1 = kWarps * slot_bytes(g);            // one unit per warp
+    // cluster split-K only as far as needed for the staged activations to fit next to a ring of depth >= 2
+    c.splits = g_force_splits ? g_force_splits : 1;
+    while (!g_force_splits && c.splits < 8 && units >= 2 * c.splits &&
+           stage_bytes(rows, K, c.splits) + 2 * ring1 > kSmemBudget) c.splits <<= 1;
+    c.depth = (kSmemBudget - stage_bytes(rows, K, c.splits)) / ring1;
+    if (c.depth > kDepth) c.depth = kDepth;
+    if (g_force_depth && g_force_depth < c.depth) c.depth = g_force_depth;
+    // out-feature tiles per CTA: about one CTA per SM in a single wave
+    c.wn = 1;
+    while (c.wn < kWarps && (long long)((n_tiles + c.wn - 1) / c.wn) * c.splits > 148) c.wn <<= 1;
+    // every K slice of a CTA should own at least one 128-k unit
+    while (c.wn < kWarps && (kWarps / c.wn) * c.splits > units) c.wn <<= 1;
     if (g_force_wn) c.wn = g_force_wn;
-    if (g_force_splits) c.splits = g_force_splits;
     return c;
 }
 
-template <int TG, int G>
-int launch_instance(const SkinnyParams& p, dim3 grid, size_t smem, cudaStream_t st)
+template <int TG, int G, int kWarps>
+int launch_instance(const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, size_t smem, cudaStream_t st)
 {
     static int configured_dev[64] = {0};   // benign race: the attribute call is idempotent
     int dev = 0;
@@ -267,68 +438,91 @@ int launch_instance(const SkinnyParams& p, dim3 grid, size_t smem, cudaStream_t 
     }
     if (dev < 64 && (int)smem > max_optin[dev]) return W4A16_ERR_BAD_SHAPE;
     if (dev >= 64 || configured_dev[dev] < (int)smem) {
-        e = cudaFuncSetAttribute(skinny_kernel<TG, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(skinny_kernel<TG, G, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev < 64) configured_dev[dev] = (int)smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = grid.y;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, skinny_kernel<TG, G>, p);
+    cfg.numAttrs = p.pdl ? 2 : 1;
+    e = cudaLaunchKernelEx(&cfg, skinny_kernel<TG, G, kWarps>, wmap, p);
     count_launch();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
 
 template <int G>
-int launch_g(int tg, const SkinnyParams& p, dim3 grid, size_t smem, cudaStream_t st)
+int launch_g(int tg, const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, size_t ring_bytes, cudaStream_t st)
 {
+    const size_t smem = (size_t)p.ring_offset + ring_bytes;
     switch (tg) {
-        case 1: return launch_instance<1, G>(p, grid, smem, st);
-        case 2: return launch_instance<2, G>(p, grid, smem, st);
-        default: return launch_instance<4, G>(p, grid, smem, st);
+        case 1: return launch_instance<1, G, 16>(wmap, p, grid, smem, st);
+        case 2: return launch_instance<2, G, 16>(wmap, p, grid, smem, st);
+        default: return launch_instance<4, G, 16>(wmap, p, grid, smem, st);
     }
 }
 
 }  // namespace
 
+void skinny_set_timeline(unsigned long long* buf) { g_timeline = buf; }
+
 void skinny_force_config(int wn, int splits)
 {
-    g_force_wn = wn;
-    g_force_splits = splits;
+    g_force_wn = wn & 0xff;
+    g_debug_mode = (wn >> 8) & 0xff;
+    g_force_splits = splits & 0xff;
+    g_force_depth = (splits >> 8) & 0xff;
+    g_force_warps = (splits >> 16) & 0xff;
 }
 
 int launch_skinny(const GemmArgs& a, cudaStream_t st)
 {
     if (a.tokens == 0) return W4A16_OK;
-    Config c = pick_config(a.tokens, a.N, a.K);
+    Config c = pick_config(a.tokens, a.N, a.K, a.g);
+    if (c.depth < 2) return W4A16_ERR_BAD_SHAPE;         // forced configuration does not fit in shared memory
     const int units = (a.K + kUnitK - 1) / kUnitK;
     if (c.splits > units) c.splits = 1;
-    if (c.wn != 1 && c.wn != 2 && c.wn != 4 && c.wn != 8) return W4A16_ERR_BAD_ALGO;
+    const int kWarps = c.warps;
+    if (c.wn != 1 && c.wn != 2 && c.wn != 4 && c.wn != 8 && c.wn != 16 && c.wn != 32) return W4A16_ERR_BAD_ALGO;
+    if (c.wn > kWarps) return W4A16_ERR_BAD_ALGO;
     if (c.splits != 1 && c.splits != 2 && c.splits != 4 && c.splits != 8) return W4A16_ERR_BAD_ALGO;
 
     SkinnyParams p;
     p.x = a.x; p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out;
-    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits;
+    p.error = device_error_word();
+    if (!p.error) return W4A16_ERR_CUDA;
+    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
     const int tok = 8 * c.tg;
-    const size_t smem = (size_t)tok * p.xs_stride * sizeof(__half) + (size_t)kWarps * kTileN * tok * sizeof(float);
+    const int rows = a.tokens < tok ? a.tokens : tok;
+    p.ring_offset = kHeaderBytes + (int)(((size_t)rows * p.xs_stride * sizeof(__half) + 127) / 128 * 128);
     const int n_tiles = a.N / kTileN;
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
+    // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words
+    CUtensorMap wmap;
+    {
+        const uint64_t dims[2] = {(uint64_t)n_tiles * 128, (uint64_t)(a.K / kTileK)};
+        const uint64_t stride_bytes = (uint64_t)n_tiles * 512;
+        const uint32_t box[2] = {128, (uint32_t)kUnitTiles};
+        int s = encode_tensor_map_2d(&wmap, a.qw, /*u32*/ 4, dims, stride_bytes, box, /*swizzle128*/ false);
+        if (s != W4A16_OK) return s;
+    }
     switch (a.g) {
-        case 128: return launch_g<128>(c.tg, p, grid, smem, st);
-        case 64:  return launch_g<64>(c.tg, p, grid, smem, st);
-        case 32:  return launch_g<32>(c.tg, p, grid, smem, st);
+        case 128: return launch_g<128>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<128>), st);
+        case 64:  return launch_g<64>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<64>), st);
+        case 32:  return launch_g<32>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<32>), st);
         default:  return W4A16_ERR_GROUP_SIZE;
     }
 }

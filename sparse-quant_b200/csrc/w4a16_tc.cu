@@ -290,23 +290,6 @@ __global__ void __launch_bounds__(128, 1) tmem_layout_probe_kernel(uint32_t* out
     if (warp == 0) tmem_dealloc(base, 32);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)f;
-    }
-    return fn;
-}
-
 int g_force_tok = 0;
 
 int pick_tok(int tokens, int N, int K)
@@ -326,21 +309,6 @@ int pick_tok(int tokens, int N, int K)
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = t; }
     }
     return best;
-}
-
-// per-device error word (allocated once; the kernels only ever write 1 into it)
-int* error_word()
-{
-    static int* words[64] = {nullptr};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return nullptr;
-    if (!words[dev]) {
-        int* p = nullptr;
-        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-        if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return nullptr;
-        words[dev] = p;
-    }
-    return words[dev];
 }
 
 template <int TOK>
@@ -372,31 +340,19 @@ bool tc_supported(int tokens, int N, int K, int g)
 
 size_t tc_workspace_bytes(int, int, int, int) { return 0; }
 
-int tc_error_state(int* host_out)
-{
-    int* w = error_word();
-    if (!w) return W4A16_ERR_CUDA;
-    cudaError_t e = cudaMemcpy(host_out, w, sizeof(int), cudaMemcpyDeviceToHost);
-    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
-}
-
 int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
 {
-    EncodeTiledFn encode = get_encode_fn();
-    if (!encode) return W4A16_ERR_CUDA;
-    int* err = error_word();
+    int* err = device_error_word();
     if (!err) return W4A16_ERR_CUDA;
     const int tok = pick_tok(a.tokens, a.N, a.K);
 
     CUtensorMap map;
-    const cuuint64_t dims[2]    = {(cuuint64_t)a.K, (cuuint64_t)a.tokens};
-    const cuuint64_t strides[1] = {(cuuint64_t)a.K * sizeof(__half)};
-    const cuuint32_t box[2]     = {(cuuint32_t)kBlockK, (cuuint32_t)tok};
-    const cuuint32_t estr[2]    = {1, 1};
-    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.x, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue);
+    {
+        const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.tokens};
+        const uint32_t box[2] = {(uint32_t)kBlockK, (uint32_t)tok};
+        int s = encode_tensor_map_2d(&map, a.x, 2, dims, (uint64_t)a.K * sizeof(__half), box, /*swizzle128*/ true);
+        if (s != W4A16_OK) return s;
+    }
 
     TcParams p;
     p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out; p.error = err;
@@ -423,8 +379,6 @@ int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
 
 }  // namespace w4a16
 
-// Reads (and leaves set) the device error word the tcgen05 kernel raises when one of its
-// bounded waits times out.  Synchronises the device.  *flag = 0 means no kernel ever gave up.
 // Debug aid: fills out[128][32] (device, uint32) with the tags read back by the probe kernel above.
 extern "C" int w4a16_debug_tmem_layout(void* out, void* stream)
 {
@@ -433,10 +387,4 @@ extern "C" int w4a16_debug_tmem_layout(void* out, void* stream)
     w4a16::count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : w4a16::record_cuda_error(e);
-}
-
-extern "C" int w4a16_tc_error_flag(int* flag)
-{
-    if (!flag) return W4A16_ERR_NULL_POINTER;
-    return w4a16::tc_error_state(flag);
 }

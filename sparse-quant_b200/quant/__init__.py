@@ -37,6 +37,7 @@ C_ABI = {
     "w4a16_last_cuda_error": (_ci, []),
     "w4a16_gemm": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
+    "w4a16_gemm_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
     "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
     "w4a16_dequant": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "w4a16_transpose_merge_zeros_scales": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
@@ -45,8 +46,9 @@ C_ABI = {
     "w4a16_gemm_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_launch_count": (ctypes.c_ulonglong, []),
     "w4a16_version": (_ci, []),
-    "w4a16_tc_error_flag": (_ci, [ctypes.POINTER(_ci)]),
+    "w4a16_device_error_flag": (_ci, [ctypes.POINTER(_ci)]),
     "w4a16_debug_tmem_layout": (_ci, [_vp, _vp]),
+    "w4a16_debug_skinny_timeline": (None, [_vp]),
     "w4a16_tune_skinny": (None, [_ci, _ci]),
     "w4a16_tune_tc": (None, [_ci, _ci]),
 }
@@ -106,11 +108,17 @@ def launch_count() -> int:
     return int(load_library().w4a16_launch_count())
 
 
-def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None):
+FLAG_STATIC_WEIGHTS = 1
+
+
+def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None,
+                  static_weights: bool = False):
     """gemm_awq_ut with the fp16 bias add of WALinear.forward fused into the kernel epilogue.
 
     I fp16 [b, s, K] (CUDA, contiguous); W int32 [K, N/8] tile-ordered; W_zeros_scales fp16
     [K/g, 2N]; bias fp16 with N elements or None.  Returns fp16 [b, s, N].
+    static_weights=True passes W4A16_FLAG_STATIC_WEIGHTS (see include/w4a16_b200.h): only for weights
+    that were written before anything still in flight on the current stream was enqueued.
     """
     _check_tensor(I, "I", dtype=torch.float16, dims=3)
     _check_tensor(W, "W", dims=2)
@@ -136,10 +144,11 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
     with torch.cuda.device(I.device):
         ws_bytes = lib.w4a16_workspace_bytes(tokens, N, K, group_size)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=I.device) if ws_bytes else None
-        st = lib.w4a16_gemm_algo(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
-                                 bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                 tokens, N, K, group_size,
-                                 ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo))
+        st = lib.w4a16_gemm_ex(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                               bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                               tokens, N, K, group_size,
+                               ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo),
+                               FLAG_STATIC_WEIGHTS if static_weights else 0)
     _check(st, "gemm_awq_ut")
     return out
 

@@ -27,6 +27,10 @@ class WALinear(nn.Module):
         self.w_bit = w_bit
         self.a_bit = a_bit
         self.group_size = group_size
+        # True: the packed buffers are not being (re)written by work still in flight on the stream that runs
+        # forward(), so the decode kernel may prefetch them while the previous kernel drains.  from_float()
+        # leaves it False until the first synchronisation point; model builders switch it on after loading.
+        self.static_weights = False
         self.register_buffer("zeros_scales", torch.zeros(in_features // group_size, out_features * 2,
                                                           dtype=torch.float16, device=dev))
         self.register_buffer("weight", torch.zeros(in_features, out_features * w_bit // 32, dtype=dtype, device=dev))
@@ -43,7 +47,8 @@ class WALinear(nn.Module):
         x3 = x if x.dim() == 3 else x.reshape(1, -1, shape[-1])
         if not x3.is_contiguous():
             x3 = x3.contiguous()
-        y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size)
+        y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size,
+                          static_weights=self.static_weights)
         return y if x.dim() == 3 else y.reshape(*shape[:-1], self.out_features)
 
     @staticmethod

@@ -55,7 +55,7 @@ def test_skinny_opt_shapes(K, N, M):
     run(M, N, K, 128, algo=1)
 
 
-@pytest.mark.parametrize("wn,splits", [(1, 1), (1, 8), (2, 4), (4, 2), (8, 1), (8, 8), (2, 1)])
+@pytest.mark.parametrize("wn,splits", [(1, 1), (1, 8), (2, 4), (4, 2), (8, 1), (8, 8), (2, 1), (16, 1), (16, 4)])
 def test_skinny_every_decomposition(wn, splits):
     import quant
     lib = quant.load_library()
@@ -92,7 +92,7 @@ def test_tc_parity(N, K, g, M):
     run(M, N, K, g, algo=2, bias=(M % 2 == 1))
     import quant
     flag = __import__("ctypes").c_int(-1)
-    assert quant.load_library().w4a16_tc_error_flag(flag) == 0 and flag.value == 0
+    assert quant.load_library().w4a16_device_error_flag(flag) == 0 and flag.value == 0
 
 
 @pytest.mark.parametrize("tile", [64, 128, 256])
@@ -197,6 +197,37 @@ def test_non_default_stream_and_graph_replay():
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(eager, out)
+
+
+def test_static_weights_flag_dependent_chain():
+    """W4A16_FLAG_STATIC_WEIGHTS (programmatic dependent launch): a chain in which every call consumes
+    the previous call's output gives the same bits as the plain launches, eagerly and in a CUDA graph."""
+    import quant
+    N = K = 1024
+    g = 128
+    ps = [make_packed(N, K, g, seed=50 + i) for i in range(3)]
+    devs = [to_dev(p) for p in ps]
+    x = (make_x(4, K) * 0.5).cuda()
+
+    def chain(static, bufs=None):
+        h = x
+        for i in range(6):
+            qw, zs = devs[i % 3]
+            h = quant.gemm_awq_bias(h, qw, zs, None, N, g, static_weights=static, out=None if bufs is None else bufs[i])
+        return h
+
+    plain = chain(False)
+    pdl = chain(True)
+    assert torch.equal(plain, pdl)
+    bufs = [torch.empty(1, 4, N, dtype=torch.float16, device="cuda") for _ in range(6)]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain(True, bufs)
+    for b in bufs:
+        b.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[5], plain)
 
 
 def test_walinear_module_and_host_buffer_entry_point():

@@ -90,6 +90,17 @@ def test_dequant_matches_reference_kernel_identity_trick(i):
     assert np.array_equal(wz, rz)
 
 
+def _self_consistent_rows(ref, x, w_ident, K):
+    """Rows of a reference-kernel output that agree with the reference's OWN dequantised weight
+    (read back through its identity-matrix GEMM) multiplied in float64.  Rebuilt unmodified for
+    sm_100a, the reference kernel returns wrong token rows for some of its tile configurations
+    (observed: N=256 K=512, tokens 16 -> rows 0-7, tokens 40 -> rows 0-31); those rows cannot pin
+    anything and are excluded - and counted."""
+    truth = x[0].double().numpy() @ w_ident.astype(np.float64).T
+    bound = 1e-2 * float(x.abs().max()) * np.sqrt(K) * float(np.abs(w_ident.astype(np.float32)).max())
+    return np.abs(ref.astype(np.float64) - truth).max(axis=1) <= bound
+
+
 @needs_cuda_golden
 @pytest.mark.parametrize("i", CASES)
 def test_gemm_within_tolerance_of_reference_kernel(i):
@@ -97,11 +108,35 @@ def test_gemm_within_tolerance_of_reference_kernel(i):
         pytest.skip("reference kernel has no tile config for this case")
     N, K, g, seed, std = QUANT_CASES[i]
     w = oracle.dequant(GOLD_C[f"c{i}_lmdeploy"], GOLD_C[f"c{i}_zs"], K, N, g)
+    w_ident = GOLD_C[f"c{i}_identity"].view(np.float16)
+    checked = 0
     for M in GEMM_TOKENS:
         x = seeded_x(M, K, seed)
-        mine = oracle.gemm_f16(x, w)
-        ref = GOLD_C[f"c{i}_gemm_m{M}"].view(np.float16)
-        check_gemm_tolerance(mine.astype(np.float32), ref.astype(np.float32), x, w, K)
+        mine = oracle.gemm_f16(x, w).astype(np.float32)
+        ref = GOLD_C[f"c{i}_gemm_m{M}"].view(np.float16).astype(np.float32)
+        ok = _self_consistent_rows(ref, x, w_ident, K)
+        # the oracle itself must be consistent on every row
+        assert _self_consistent_rows(mine, x, w_ident, K).all()
+        if ok.any():
+            check_gemm_tolerance(mine[ok], ref[ok], x, w, K)
+            checked += int(ok.sum())
+    assert checked >= sum(GEMM_TOKENS) // 3
+
+
+@needs_cuda_golden
+def test_reference_kernel_bad_rows_are_the_known_ones():
+    """Documents (and bounds) where the rebuilt reference kernel disagrees with its own weights."""
+    bad = {}
+    for i, (N, K, g, seed, std) in enumerate(QUANT_CASES):
+        if f"c{i}_gemm_m1" not in GOLD_C:
+            continue
+        w_ident = GOLD_C[f"c{i}_identity"].view(np.float16)
+        for M in GEMM_TOKENS:
+            ref = GOLD_C[f"c{i}_gemm_m{M}"].view(np.float16).astype(np.float32)
+            ok = _self_consistent_rows(ref, seeded_x(M, K, seed), w_ident, K)
+            if not ok.all():
+                bad[(N, K, M)] = np.where(~ok)[0].tolist()
+    assert set(bad) <= {(256, 512, 16), (256, 512, 40)}, bad
 
 
 def test_fp16_primitives_against_torch():
