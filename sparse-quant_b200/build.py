@@ -36,6 +36,8 @@ def build(force=False, verbose=False):
     cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-Xcompiler", "-fPIC", "-shared", "--threads", "0",
            "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", OUT] + sources()
+    if os.environ.get("W4A16_DEBUG"):
+        cmd.insert(1, "-DW4A16_SKINNY_DEBUG")    # phase time stamps / experiment switches in the decode kernel
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd))

@@ -8,11 +8,11 @@
 // whole machine streams the weight matrix once, in one wave of one 512-thread CTA per SM:
 //
 //   * a warp owns one 32-wide out-feature tile and a contiguous K slice.  Its lane 0 keeps a
-//     private ring of TMA copies in flight into shared memory, four 128-k units deep: per unit one
-//     tensor copy (a 4-row box of the packed matrix seen as [K/32][N/32 x 512 B]: four strided
-//     512-byte tiles in one operation) plus one 128-byte bulk copy of the group's (zero, scale)
-//     pairs, both completing on the unit's own mbarrier - about 130 KB in flight per SM with no
-//     registers spent on it;
+//     private ring of TMA copies in flight into shared memory, two 256-k units deep: per unit one
+//     tensor copy (an 8-row box of the packed matrix seen as [K/32][N/32 x 512 B]: eight strided
+//     512-byte tiles in one operation) plus one 128-byte bulk copy per quantisation group of its
+//     (zero, scale) pairs, all completing on the unit's own mbarrier - about 130 KB in flight per
+//     SM with no registers spent on it;
 //   * the nibbles are expanded in registers to fp16 (64 + q) - exact - and fed straight to
 //     mma.m16n8k16 as the A fragment (the packed layout IS that fragment); activations are staged
 //     once per CTA in shared memory and read with ldmatrix as the B fragment; a second MMA with an
@@ -42,17 +42,25 @@ using namespace sm100;
 
 namespace {
 
+#ifdef W4A16_SKINNY_DEBUG
+constexpr bool kDebug = true;     // phase time stamps and experiment switches compiled in
+#else
+constexpr bool kDebug = false;
+#endif
+
 constexpr int kMaxWarps  = 32;
 constexpr int kHeaderBytes = 2048;           // zero chunk, abort flag, mbarriers
-constexpr int kUnitK     = 128;               // k per pipeline unit (4 tiles)
-constexpr int kUnitTiles = kUnitK / kTileK;
-constexpr int kDepth     = 4;                 // units in flight per warp
+constexpr int kMaxDepth  = 4;                 // most units in flight per warp
+// k per pipeline unit: 256 (8 tiles) when at most 8 tokens are staged, 128 otherwise (the staged activations
+// then need the shared memory); the ring holds 2 x 256-k or up to 4 x 128-k units per warp
+__host__ __device__ constexpr int unit_k_for(int tg) { return tg == 1 ? 256 : 128; }
+__host__ __device__ constexpr int max_depth_for(int tg) { return tg == 1 ? 2 : 4; }
 constexpr uint64_t kWaitBudgetNs = 200ull * 1000 * 1000;
 
-template <int G>
+template <int G, int UK>
 struct Slot {                                 // one pipeline unit in shared memory
-    uint4    tiles[kUnitTiles][32];           // 4 x 512 B
-    uint32_t zs[kUnitK / G][32];              // per group: (zero+64, scale) of the tile's 32 out-features
+    uint4    tiles[UK / kTileK][32];          // 512 B per 32x32 tile
+    uint32_t zs[UK / G][32];                  // per group: (zero+64, scale) of the tile's 32 out-features
 };
 
 struct SkinnyParams {
@@ -67,7 +75,7 @@ struct SkinnyParams {
     int splits;      // cluster size along K (gridDim.y)
     int xs_stride;   // halfs per staged activation row
     int ring_offset; // byte offset of the per-warp rings in shared memory
-    int depth;       // units in flight per warp (2..kDepth)
+    int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
     int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
     unsigned long long* timeline;   // debug: [cta][warp][8] globaltimer stamps, or null
@@ -76,13 +84,14 @@ struct SkinnyParams {
 
 // lane 0 of a warp: arm the slot's barrier and start the copies of one unit.  `zsrc` points at the unit's first
 // (zero, scale) row for this warp's out-feature tile.
-template <int G>
+template <int G, int kUnitK>
 __device__ __forceinline__ void issue_unit(uint32_t slot_addr, uint32_t bar, const CUtensorMap* wmap, const uint32_t* zsrc,
                                            int N, int unit, int nt, int groups)
 {
     constexpr int kGroupsPerUnit = kUnitK / G;
+    constexpr int kUnitTiles = kUnitK / kTileK;
     const int n_groups = min(kGroupsPerUnit, groups - unit * kGroupsPerUnit);     // < full only at the K edge
-    // the tensor copy always delivers the full 4 x 512 B box (rows past K/32 arrive as zeros)
+    // the tensor copy always delivers the full box of kUnitTiles x 512 B (rows past K/32 arrive as zeros)
     mbar_arrive_expect_tx(bar, kUnitTiles * 512u + n_groups * 128u);
     tma_load_2d(slot_addr, wmap, nt * 128, unit * kUnitTiles, bar);
 #pragma unroll
@@ -90,9 +99,9 @@ __device__ __forceinline__ void issue_unit(uint32_t slot_addr, uint32_t bar, con
         if (gi < n_groups) bulk_load(slot_addr + kUnitTiles * 512u + gi * 128u, zsrc + (size_t)gi * N, 128u, bar);
 }
 
-template <int TG, int G>
-__device__ __forceinline__ void compute_unit(const Slot<G>* slot, float (&acc)[TG][2][4], const uint32_t (&xaddr)[TG],
-                                             const int (&kmul)[TG], int k_local, int kt0, int k_tiles, int lane)
+template <int TG, int G, int kUnitK>
+__device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float (&acc)[TG][2][4], const uint32_t (&xaddr)[TG],
+                                             const int (&kmul)[TG], int k_local, int kt0, int k_tiles, int lane, int dbg)
 {
     constexpr int kTilesPerGroup = G / kTileK;
     constexpr uint32_t kOnes = 0x3c003c00u;
@@ -115,8 +124,13 @@ __device__ __forceinline__ void compute_unit(const Slot<G>* slot, float (&acc)[T
 #pragma unroll
                 for (int kh = 0; kh < 2; ++kh) {
                     uint32_t a0[4], a1[4];
-                    unpack_s4x8_fast(words[kh * 2 + 0], a0);
-                    unpack_s4x8_fast(words[kh * 2 + 1], a1);
+                    if (dbg & 4) {
+                        a0[0] = a0[1] = a0[2] = a0[3] = words[kh * 2 + 0];
+                        a1[0] = a1[1] = a1[2] = a1[3] = words[kh * 2 + 1];
+                    } else {
+                        unpack_s4x8_fast(words[kh * 2 + 0], a0);
+                        unpack_s4x8_fast(words[kh * 2 + 1], a1);
+                    }
 #pragma unroll
                     for (int tg = 0; tg < TG; ++tg) {
                         if (tt == 0 && kh == 0) {
@@ -132,6 +146,13 @@ __device__ __forceinline__ void compute_unit(const Slot<G>* slot, float (&acc)[T
                 }
             }
             // zero point and scale of the group, applied in fp32
+            if (dbg & 8) {
+#pragma unroll
+                for (int tg = 0; tg < TG; ++tg)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { acc[tg][0][j] += accg[tg][0][j] + xsum[tg][j]; acc[tg][1][j] += accg[tg][1][j]; }
+                continue;
+            }
 #pragma unroll
             for (int nh = 0; nh < 2; ++nh) {
                 float zf[2], sf[2];
@@ -173,8 +194,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int kTok = 8 * TG;
     constexpr int kThreads = kWarps * 32;
-    static_assert(2 * sizeof(Slot<G>) >= kTok * 33 * 4, "a warp's partial sums reuse its own ring (depth >= 2)");
-    static_assert(sizeof(Slot<G>) % 16 == 0, "bulk copies need 16-byte aligned destinations");
+    constexpr int kUnitK = unit_k_for(TG), kUnitTiles = kUnitK / kTileK, kDepth = kMaxDepth;
+    using SlotT = Slot<G, kUnitK>;
+    static_assert(2 * sizeof(SlotT) >= kTok * 33 * 4, "a warp's partial sums reuse its own ring (depth >= 2)");
+    static_assert(sizeof(SlotT) % 16 == 0, "bulk copies need 16-byte aligned destinations");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wn = p.wn, wk = kWarps / wn;
@@ -195,16 +218,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     const int n_units = nt_valid ? wu1 - wu0 : 0;
 
     // shared memory: header (kHeaderBytes): [16 B zeros][abort flag][barriers kMaxWarps x kDepth] | activations | per-warp rings
-    static_assert(32 + kMaxWarps * kDepth * 8 <= kHeaderBytes, "header overflow");
+    static_assert(32 + kMaxWarps * kMaxDepth * 8 <= kHeaderBytes, "header overflow");
     const uint32_t bars = smem_u32(smem) + 32 + warp * kDepth * 8;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 16);
     __half* xs = reinterpret_cast<__half*>(smem + kHeaderBytes);
     const int depth = p.depth;
-    const int ring_bytes = depth * (int)sizeof(Slot<G>);   // per warp
-    Slot<G>* ring = reinterpret_cast<Slot<G>*>(smem + p.ring_offset + (size_t)warp * ring_bytes);
+    const int ring_bytes = depth * (int)sizeof(SlotT);   // per warp
+    SlotT* ring = reinterpret_cast<SlotT*>(smem + p.ring_offset + (size_t)warp * ring_bytes);
 
     unsigned long long* tl = nullptr;
-    if (p.timeline && lane == 0)
+    if (kDebug && p.timeline && lane == 0)
         tl = p.timeline + ((size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kWarps + warp) * 8;
     if (tl) tl[0] = globaltimer_ns();
     if (threadIdx.x == 0) *abort_flag = 0;
@@ -218,7 +241,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     // token rows past `rows` all read the 16 zero bytes at the start of shared memory.
     const int kc0 = cu0 * kUnitK;
     const int vec_per_row = cta_units * (kUnitK / 8);
-    const int total = (p.debug_mode & 2) ? 0 : rows * vec_per_row;
+    const int total = (kDebug && (p.debug_mode & 2)) ? 0 : rows * vec_per_row;
+    const unsigned vpr_inv = vec_per_row > 1 ? 0xffffffffu / (unsigned)vec_per_row + 1u : 0u;   // i / vpr == umulhi(i, inv) for i < 2^16 * vpr
+    auto div_vpr = [&](int i) { return vec_per_row > 1 ? (int)__umulhi((unsigned)i, vpr_inv) : i; };
     constexpr int kBatch = 8;                               // 16-byte loads in flight per thread
     uint4 xval[kBatch];
     int xdst[kBatch];
@@ -229,7 +254,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             xval[j] = make_uint4(0, 0, 0, 0);
             xdst[j] = -1;
             if (i < total) {
-                const int row = i / vec_per_row, v = i - row * vec_per_row;
+                const int row = div_vpr(i), v = i - row * vec_per_row;
                 xdst[j] = row * p.xs_stride + v * 8;
                 if (kc0 + v * 8 < p.K) xval[j] = *reinterpret_cast<const uint4*>(p.x + (size_t)(tok0 + row) * p.K + kc0 + v * 8);
             }
@@ -248,7 +273,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         if (lane == 0) {
             if (warp == 0) prefetch_tmap(&wmap);
             for (int i = 0; i < depth && i < n_units; ++i)
-                issue_unit<G>(ring_addr + i * (uint32_t)sizeof(Slot<G>), bars + 8 * i, &wmap, zs_next + (size_t)i * zs_step, p.N, wu0 + i, nt, groups);
+                issue_unit<G, kUnitK>(ring_addr + i * (uint32_t)sizeof(SlotT), bars + 8 * i, &wmap, zs_next + (size_t)i * zs_step, p.N, wu0 + i, nt, groups);
         }
     };
 
@@ -302,13 +327,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             if (!ok) break;
             if (tl && i == 0) tl[3] = globaltimer_ns();
             const int u = wu0 + i;
-            if ((p.debug_mode & 1) == 0)
-                compute_unit<TG, G>(ring + slot, acc, xaddr, kmul, (u - cu0) * kUnitK, u * kUnitTiles, k_tiles, lane);
+            if (!kDebug || (p.debug_mode & 1) == 0)
+                compute_unit<TG, G, kUnitK>(ring + slot, acc, xaddr, kmul, (u - cu0) * kUnitK, u * kUnitTiles, k_tiles, lane, kDebug ? p.debug_mode : 0);
             else
                 acc[0][0][0] += __uint_as_float(ring[slot].tiles[0][lane].x & 0x3fu);
             __syncwarp();                                   // every lane is done reading the slot
             if (lane == 0 && i + depth < n_units)
-                issue_unit<G>(ring_addr + slot * (uint32_t)sizeof(Slot<G>), bars + 8 * slot, &wmap, zs_next + (size_t)(i + depth) * zs_step, p.N,
+                issue_unit<G, kUnitK>(ring_addr + slot * (uint32_t)sizeof(SlotT), bars + 8 * slot, &wmap, zs_next + (size_t)(i + depth) * zs_step, p.N,
                               u + depth, nt, groups);
             if (++slot == depth) { slot = 0; phase ^= 1u; }
         }
@@ -387,10 +412,10 @@ unsigned long long* g_timeline = nullptr;
 
 constexpr int kSmemBudget = 227 * 1024;                  // opt-in shared memory of one CTA on sm_100
 
-int slot_bytes(int g) { return kUnitTiles * 512 + (kUnitK / g) * 128; }
+int slot_bytes(int g, int uk) { return (uk / kTileK) * 512 + (uk / g) * 128; }
 
 // shared memory the activations of one CTA need: [header 1 KB][rows x (K/S + 8) halfs], 128-byte aligned
-int stage_bytes(int rows, int K, int splits)
+int stage_bytes(int rows, int K, int splits, int kUnitK)
 {
     const int units = (K + kUnitK - 1) / kUnitK;
     const int cta_units = (units + splits - 1) / splits;
@@ -401,17 +426,18 @@ Config pick_config(int tokens, int N, int K, int g)
 {
     Config c;
     c.tg = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
+    const int kUnitK = unit_k_for(c.tg);
     const int n_tiles = N / kTileN, units = (K + kUnitK - 1) / kUnitK;
     const int rows = tokens < 8 * c.tg ? tokens : 8 * c.tg;
     c.warps = 16;
     const int kWarps = c.warps;
-    const int ring1 = kWarps * slot_bytes(g);            // one unit per warp
+    const int ring1 = kWarps * slot_bytes(g, kUnitK);    // one unit per warp
     // cluster split-K only as far as needed for the staged activations to fit next to a ring of depth >= 2
     c.splits = g_force_splits ? g_force_splits : 1;
     while (!g_force_splits && c.splits < 8 && units >= 2 * c.splits &&
-           stage_bytes(rows, K, c.splits) + 2 * ring1 > kSmemBudget) c.splits <<= 1;
-    c.depth = (kSmemBudget - stage_bytes(rows, K, c.splits)) / ring1;
-    if (c.depth > kDepth) c.depth = kDepth;
+           stage_bytes(rows, K, c.splits, kUnitK) + 2 * ring1 > kSmemBudget) c.splits <<= 1;
+    c.depth = (kSmemBudget - stage_bytes(rows, K, c.splits, kUnitK)) / ring1;
+    if (c.depth > max_depth_for(c.tg)) c.depth = max_depth_for(c.tg);
     if (g_force_depth && g_force_depth < c.depth) c.depth = g_force_depth;
     // out-feature tiles per CTA: about one CTA per SM in a single wave
     c.wn = 1;
@@ -490,6 +516,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     if (a.tokens == 0) return W4A16_OK;
     Config c = pick_config(a.tokens, a.N, a.K, a.g);
     if (c.depth < 2) return W4A16_ERR_BAD_SHAPE;         // forced configuration does not fit in shared memory
+    const int kUnitK = unit_k_for(c.tg), kUnitTiles = kUnitK / kTileK;
     const int units = (a.K + kUnitK - 1) / kUnitK;
     if (c.splits > units) c.splits = 1;
     const int kWarps = c.warps;
@@ -520,9 +547,9 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
         if (s != W4A16_OK) return s;
     }
     switch (a.g) {
-        case 128: return launch_g<128>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<128>), st);
-        case 64:  return launch_g<64>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<64>), st);
-        case 32:  return launch_g<32>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * sizeof(Slot<32>), st);
+        case 128: return launch_g<128>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * slot_bytes(128, kUnitK), st);
+        case 64:  return launch_g<64>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * slot_bytes(64, kUnitK), st);
+        case 32:  return launch_g<32>(c.tg, wmap, p, grid, (size_t)kWarps * c.depth * slot_bytes(32, kUnitK), st);
         default:  return W4A16_ERR_GROUP_SIZE;
     }
 }

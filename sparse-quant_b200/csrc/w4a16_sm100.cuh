@@ -33,28 +33,28 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+// One potentially-blocking probe: the hardware suspends the thread until the phase completes or
+// `suspend_ns` elapses, so a waiting warp does not burn issue slots polling.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t suspend_ns)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(suspend_ns) : "memory");
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up; returns
 // false on timeout or when another role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+    constexpr uint32_t kSuspendNs = 1000000;                 // 1 ms per probe
+    if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
     const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > budget_ns) { *abort_flag = 1; return false; }
-        }
+    while (!mbar_try_wait(bar, parity, kSuspendNs)) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > budget_ns) { *abort_flag = 1; return false; }
     }
     return true;
 }
