@@ -203,6 +203,9 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--small", action="store_true", help="one weight set, no extras (for profiler captures)")
+    ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
+                    help="capture the step in a CUDA graph (auto: on for 1 GPU, off when NCCL collectives are in the step)")
+    ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -213,6 +216,10 @@ def main():
     import quant
     lib = quant.load_library()
     rank = int(os.environ.get("RANK", "0"))
+
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -221,41 +228,72 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        note("process group up")
 
     sets = 1 if args.small else SETS
     peaks = measured_peaks()
     stream = torch.cuda.Stream(device=dev)
     sp = stream.cuda_stream
 
-    # weights (resident), activations, outputs
+    # Tensor-parallel sharding of the sweep at N > 1 (Megatron style, as the model builder does it):
+    #   4096 x 4096  (q/k/v-type) and 4096 x 16384 (fc1): column-parallel, each rank owns N / world out-features;
+    #   16384 x 4096 (fc2): row-parallel, each rank owns K / world in-features and the [M, 4096] fp16 partial
+    #   outputs are summed with one NCCL all-reduce per call.  Total work is fixed: strong scaling.
+    def local_shape(K, N):
+        if world == 1:
+            return K, N, False
+        if K > N:
+            return K // world, N, True            # row-parallel -> all-reduce
+        return K, N // world, False               # column-parallel
+
     weights = {}
     for si, (K, N) in enumerate(DECODE_SHAPES):
-        weights[(K, N)] = [synth_packed(K, N, G, dev, 1234 + 10 * si + s) for s in range(sets)]
-    xs = {(M, K): torch.randn(M, K, device=dev, dtype=torch.float16) for M in DECODE_M for K in (4096, 16384)}
-    outs = {(M, N): torch.empty(M, N, device=dev, dtype=torch.float16) for M in DECODE_M for N in (4096, 16384)}
+        kl, nl, _ = local_shape(K, N)
+        weights[(K, N)] = [synth_packed(kl, nl, G, dev, 1234 + 10 * si + s + 100 * rank) for s in range(sets)]
+    xs, outs = {}, {}
+    for (K, N) in DECODE_SHAPES:
+        kl, nl, _ = local_shape(K, N)
+        for M in DECODE_M:
+            xs[(M, K, N)] = torch.randn(M, kl, device=dev, dtype=torch.float16)
+            outs[(M, K, N)] = torch.empty(M, nl, device=dev, dtype=torch.float16)
 
     def launch(M, K, N, s, st):
         qw, zs = weights[(K, N)][s]
+        kl, nl, reduce = local_shape(K, N)
         # the packed weights are static module state: W4A16_FLAG_STATIC_WEIGHTS lets a launch prefetch them while
         # the previous kernel of the stream drains (x and out still wait for it)
-        r = lib.w4a16_gemm_ex(xs[(M, K)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, N)].data_ptr(),
-                              M, N, K, G, None, 0, st, 0, 1)
+        r = lib.w4a16_gemm_ex(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
+                              M, nl, kl, G, None, 0, st, 0, 1)
         if r != 0:
             raise RuntimeError(lib.w4a16_status_str(r).decode())
+        if reduce:
+            dist.all_reduce(outs[(M, K, N)])
 
     calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
     step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
     launches_per_step = len(calls)
+    collectives_per_step = sum(1 for (M, K, N, s) in calls if local_shape(K, N)[2])
 
     # one eager pass (per-device attribute set-up happens here, outside capture), then capture the step
     with torch.cuda.stream(stream):
         for c in calls:
             launch(*c, sp)
     stream.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        for c in calls:
-            launch(*c, torch.cuda.current_stream().cuda_stream)
+    note("eager pass done")
+    use_graph = args.graph == "on" or (args.graph == "auto" and world == 1)
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for c in calls:
+                launch(*c, torch.cuda.current_stream().cuda_stream)
+        note("graph captured")
+
+        def run_step():
+            graph.replay()
+    else:
+        def run_step():
+            for c in calls:
+                launch(*c, sp)
 
     def barrier():
         if dist is not None:
@@ -264,8 +302,9 @@ def main():
 
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
-            graph.replay()
+            run_step()
     barrier()
+    note("warm-up done")
     sampler = ClockSampler(local)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -273,9 +312,10 @@ def main():
     with torch.cuda.stream(stream):
         e0.record(stream)
         for _ in range(args.steps):
-            graph.replay()
+            run_step()
         e1.record(stream)
     barrier()
+    note("timed region done")
     t1 = time.perf_counter()
     clocks = sampler.finish(t0, t1)
     ms = e0.elapsed_time(e1)
@@ -283,32 +323,36 @@ def main():
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    total_bytes = step_bytes * args.steps * world
+    total_bytes = step_bytes * args.steps          # the whole (unsharded) sweep, whatever the number of ranks
     value = total_bytes / (ms * 1e-3) / 1e9
     per_gpu = value / world
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16xs4->f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "weight_sets": sets, "launches_per_step": launches_per_step,
                    "l2": f"inputs larger than L2: {sets} rotating weight sets, {step_bytes / 1e6:.0f} MB touched per step",
-                   "timing": "CUDA graph of one step, K replays between CUDA events on the launching stream",
-                   "multi_gpu": "independent replicas, no collective" if world > 1 else "single GPU"},
+                   "timing": ("CUDA graph of one step, K replays between CUDA events on the launching stream" if use_graph else
+                              "stream-ordered launches (no graph), K steps between CUDA events on the launching stream"),
+                   "multi_gpu": (f"tensor parallel over {world} ranks: column-parallel 4096x4096 and 4096x16384, row-parallel "
+                                 f"16384x4096 with {collectives_per_step} NCCL fp16 all-reduces of [M,4096] per step") if world > 1 else "single GPU"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
     line["roofline"] = {
         "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
         "traffic": None, "kernel": "skinny_kernel", "peak_source": f"of {peaks['source']} (copy bandwidth)",
-        "algorithmic_bytes_per_launch": step_bytes / launches_per_step,
+        "algorithmic_bytes_per_launch": step_bytes / launches_per_step / world,
         "avg_launch_us": 1e3 * ms / (args.steps * launches_per_step),
     }
 
+    e2e = None if args.small else e2e_host(lib, weights, dev, stream, sets, world, local_shape)
     if rank == 0 and not args.small:
-        line["sweep"] = decode_sweep(lib, weights, xs, outs, stream, sets, peaks)
-        line["e2e"] = e2e_host(lib, weights, dev, stream, sets, world)
-        if not args.no_prefill:
+        if world == 1:
+            line["sweep"] = decode_sweep(lib, weights, xs, outs, stream, sets, peaks)
+        line["e2e"] = e2e
+        if not args.no_prefill and world == 1:
             line["prefill"] = prefill_sweep(lib, weights, dev, stream, sets, peaks)
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(repeat=5)
@@ -361,7 +405,7 @@ def decode_sweep(lib, weights, xs, outs, stream, sets, peaks):
         for M in DECODE_M:
             def fn(i, sp=sp, M=M, K=K, N=N):
                 qw, zs = weights[(K, N)][i % sets]
-                lib.w4a16_gemm_ex(xs[(M, K)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, N)].data_ptr(),
+                lib.w4a16_gemm_ex(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
                                   M, N, K, G, None, 0, sp, 0, 1)
             ms = time_graph(fn, stream, 5 * sets, 10)
             gbs = decode_bytes(M, K, N) / (ms * 1e-3) / 1e9
@@ -369,21 +413,27 @@ def decode_sweep(lib, weights, xs, outs, stream, sets, peaks):
     return rows
 
 
-def e2e_host(lib, weights, dev, stream, sets, world):
+def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
     """The same sweep through w4a16_gemm_host: x from pinned host memory, y back to pinned host memory,
-    both copies inside the timed region; the packed weights stay resident (module state)."""
+    both copies inside the timed region; the packed weights stay resident (module state).  With several
+    ranks every rank runs its shard through the host-buffer call (rank 0 reports; no collective here)."""
     sp = stream.cuda_stream
-    xh = {(M, K): torch.randn(M, K).half().pin_memory() for M in DECODE_M for K in (4096, 16384)}
-    oh = {(M, N): torch.empty(M, N, dtype=torch.float16).pin_memory() for M in DECODE_M for N in (4096, 16384)}
-    xd = {k: torch.empty(k, dtype=torch.float16, device=dev) for k in xh}
-    od = {k: torch.empty(k, dtype=torch.float16, device=dev) for k in oh}
+    xh, oh, xd, od = {}, {}, {}, {}
+    for (K, N) in DECODE_SHAPES:
+        kl, nl, _ = local_shape(K, N)
+        for M in DECODE_M:
+            xh[(M, K, N)] = torch.randn(M, kl).half().pin_memory()
+            oh[(M, K, N)] = torch.empty(M, nl, dtype=torch.float16).pin_memory()
+            xd[(M, K, N)] = torch.empty(M, kl, dtype=torch.float16, device=dev)
+            od[(M, K, N)] = torch.empty(M, nl, dtype=torch.float16, device=dev)
     calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
 
     def one(c):
         M, K, N, s = c
         qw, zs = weights[(K, N)][s]
-        r = lib.w4a16_gemm_host(xh[(M, K)].data_ptr(), oh[(M, N)].data_ptr(), xd[(M, K)].data_ptr(), od[(M, N)].data_ptr(),
-                                qw.data_ptr(), zs.data_ptr(), None, M, N, K, G, None, 0, sp)
+        kl, nl, _ = local_shape(K, N)
+        r = lib.w4a16_gemm_host(xh[(M, K, N)].data_ptr(), oh[(M, K, N)].data_ptr(), xd[(M, K, N)].data_ptr(),
+                                od[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, M, nl, kl, G, None, 0, sp)
         if r != 0:
             raise RuntimeError(lib.w4a16_status_str(r).decode())
 
@@ -401,8 +451,8 @@ def e2e_host(lib, weights, dev, stream, sets, world):
     stream.synchronize()
     wall = time.perf_counter() - t0
     step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
-    h2d = sum(M * K * 2 for (M, K, N, s) in calls)
-    d2h = sum(M * N * 2 for (M, K, N, s) in calls)
+    h2d = sum(M * local_shape(K, N)[0] * 2 for (M, K, N, s) in calls)
+    d2h = sum(M * local_shape(K, N)[1] * 2 for (M, K, N, s) in calls)
     return {"value": step_bytes * steps / wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "steps": steps, "ms_per_step": 1e3 * wall / steps, "timer": "host wall clock around synchronous calls",
             "device_event_ms_per_step": e0.elapsed_time(e1) / steps}
