@@ -74,6 +74,7 @@ struct SkinnyParams {
     int wn;          // out-feature tiles per CTA (1,2,4,8,16); WK = 16 / wn K-slices per CTA
     int splits;      // cluster size along K (gridDim.y)
     int xs_stride;   // halfs per staged activation row
+    int xsum_offset; // byte offset of the per-group activation sums [groups of the CTA][tokens] fp32
     int ring_offset; // byte offset of the per-warp rings in shared memory
     int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
@@ -101,17 +102,17 @@ __device__ __forceinline__ void issue_unit(uint32_t slot_addr, uint32_t bar, con
 
 template <int TG, int G, int kUnitK>
 __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float (&acc)[TG][2][4], const uint32_t (&xaddr)[TG],
-                                             const int (&kmul)[TG], int k_local, int kt0, int k_tiles, int lane, int dbg)
+                                             const int (&kmul)[TG], int k_local, int kt0, int k_tiles, int lane, int dbg,
+                                             const float* xsum_s)
 {
     constexpr int kTilesPerGroup = G / kTileK;
     constexpr uint32_t kOnes = 0x3c003c00u;
-    const uint32_t ones[4] = {kOnes, kOnes, kOnes, kOnes};
-    const int r = lane >> 2;
+    const int r = lane >> 2, c = lane & 3;
 #pragma unroll
     for (int gi = 0; gi < kUnitK / G; ++gi) {
         if (kt0 + gi * kTilesPerGroup < k_tiles) {                  // warp-uniform: the group exists
-            // three accumulator chains (sum x, out-features 0-15, 16-31) interleaved per 16-k half
-            float accg[TG][2][4], xsum[TG][4];
+            // two accumulator chains (out-features 0-15, 16-31) per token group, interleaved per 16-k half
+            float accg[TG][2][4];
 #pragma unroll
             for (int tt = 0; tt < kTilesPerGroup; ++tt) {
                 const int t = gi * kTilesPerGroup + tt;
@@ -134,23 +135,28 @@ __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float 
 #pragma unroll
                     for (int tg = 0; tg < TG; ++tg) {
                         if (tt == 0 && kh == 0) {
-                            mma_m16n8k16_zc(xsum[tg], ones, b[tg][0], b[tg][1]);
                             mma_m16n8k16_zc(accg[tg][0], a0, b[tg][0], b[tg][1]);
                             mma_m16n8k16_zc(accg[tg][1], a1, b[tg][0], b[tg][1]);
                         } else {
-                            mma_m16n8k16(xsum[tg], ones, b[tg][2 * kh], b[tg][2 * kh + 1]);
                             mma_m16n8k16(accg[tg][0], a0, b[tg][2 * kh], b[tg][2 * kh + 1]);
                             mma_m16n8k16(accg[tg][1], a1, b[tg][2 * kh], b[tg][2 * kh + 1]);
                         }
                     }
                 }
             }
-            // zero point and scale of the group, applied in fp32
+            // zero point and scale of the group, applied in fp32; sum_k x of the group was precomputed per CTA
+            float xsum[TG][2];
+#pragma unroll
+            for (int tg = 0; tg < TG; ++tg) {
+                const float2 v = *reinterpret_cast<const float2*>(xsum_s + (k_local / G + gi) * (8 * TG) + tg * 8 + 2 * c);
+                xsum[tg][0] = v.x;
+                xsum[tg][1] = v.y;
+            }
             if (dbg & 8) {
 #pragma unroll
                 for (int tg = 0; tg < TG; ++tg)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { acc[tg][0][j] += accg[tg][0][j] + xsum[tg][j]; acc[tg][1][j] += accg[tg][1][j]; }
+                    for (int j = 0; j < 4; ++j) { acc[tg][0][j] += accg[tg][0][j]; acc[tg][1][j] += accg[tg][1][j]; }
                 continue;
             }
 #pragma unroll
@@ -298,6 +304,34 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     }
     if (tl) tl[1] = globaltimer_ns();
     __syncthreads();
+
+    // sum_k x[t, k] per quantisation group of this CTA's K range, once per CTA: an MMA with an all-ones A
+    // fragment over the staged activations (every row of the result holds the sums), groups dealt round-robin
+    // to the warps; the main loop reads them back when it applies the zero points.
+    {
+        float* xsum_w = reinterpret_cast<float*>(smem + p.xsum_offset);
+        const int cta_groups = (min(cu1 * kUnitK, p.K) - cu0 * kUnitK) / G;
+        constexpr uint32_t kOnes = 0x3c003c00u;
+        const uint32_t ones[4] = {kOnes, kOnes, kOnes, kOnes};
+        for (int gidx = warp; gidx < cta_groups; gidx += kWarps) {
+#pragma unroll
+            for (int tg = 0; tg < TG; ++tg) {
+                const int row = tg * 8 + (lane & 7);
+                const bool real = row < rows;
+                const uint32_t base = real ? smem_u32(xs) + (uint32_t)((row * p.xs_stride + (lane >> 3) * 8 + gidx * G) * 2) : smem_u32(smem);
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int t = 0; t < G / kTileK; ++t) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, base + (real ? t * kTileK * 2 : 0));
+                    mma_m16n8k16(sum, ones, b[0], b[1]);
+                    mma_m16n8k16(sum, ones, b[2], b[3]);
+                }
+                if (lane < 4) *reinterpret_cast<float2*>(xsum_w + gidx * kTok + tg * 8 + 2 * lane) = make_float2(sum[0], sum[1]);
+            }
+        }
+    }
+    __syncthreads();
     if (tl) tl[2] = globaltimer_ns();
 
     float acc[TG][2][4];
@@ -328,7 +362,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             if (tl && i == 0) tl[3] = globaltimer_ns();
             const int u = wu0 + i;
             if (!kDebug || (p.debug_mode & 1) == 0)
-                compute_unit<TG, G, kUnitK>(ring + slot, acc, xaddr, kmul, (u - cu0) * kUnitK, u * kUnitTiles, k_tiles, lane, kDebug ? p.debug_mode : 0);
+                compute_unit<TG, G, kUnitK>(ring + slot, acc, xaddr, kmul, (u - cu0) * kUnitK, u * kUnitTiles, k_tiles, lane, kDebug ? p.debug_mode : 0,
+                                            reinterpret_cast<const float*>(smem + p.xsum_offset));
             else
                 acc[0][0][0] += __uint_as_float(ring[slot].tiles[0][lane].x & 0x3fu);
             __syncwarp();                                   // every lane is done reading the slot
@@ -415,11 +450,23 @@ constexpr int kSmemBudget = 227 * 1024;                  // opt-in shared memory
 int slot_bytes(int g, int uk) { return (uk / kTileK) * 512 + (uk / g) * 128; }
 
 // shared memory the activations of one CTA need: [header 1 KB][rows x (K/S + 8) halfs], 128-byte aligned
-int stage_bytes(int rows, int K, int splits, int kUnitK)
+int xs_bytes(int rows, int K, int splits, int kUnitK)
 {
     const int units = (K + kUnitK - 1) / kUnitK;
     const int cta_units = (units + splits - 1) / splits;
-    return kHeaderBytes + (int)(((size_t)rows * (cta_units * kUnitK + 8) * sizeof(__half) + 127) / 128 * 128);
+    return (int)(((size_t)rows * (cta_units * kUnitK + 8) * sizeof(__half) + 127) / 128 * 128);
+}
+
+int xsum_bytes(int tg, int K, int splits, int kUnitK, int g)
+{
+    const int units = (K + kUnitK - 1) / kUnitK;
+    const int cta_units = (units + splits - 1) / splits;
+    return ((cta_units * kUnitK / g) * 8 * tg * (int)sizeof(float) + 127) / 128 * 128;
+}
+
+int stage_bytes(int rows, int K, int splits, int kUnitK, int tg, int g)
+{
+    return kHeaderBytes + xs_bytes(rows, K, splits, kUnitK) + xsum_bytes(tg, K, splits, kUnitK, g);
 }
 
 Config pick_config(int tokens, int N, int K, int g)
@@ -435,8 +482,8 @@ Config pick_config(int tokens, int N, int K, int g)
     // cluster split-K only as far as needed for the staged activations to fit next to a ring of depth >= 2
     c.splits = g_force_splits ? g_force_splits : 1;
     while (!g_force_splits && c.splits < 8 && units >= 2 * c.splits &&
-           stage_bytes(rows, K, c.splits, kUnitK) + 2 * ring1 > kSmemBudget) c.splits <<= 1;
-    c.depth = (kSmemBudget - stage_bytes(rows, K, c.splits, kUnitK)) / ring1;
+           stage_bytes(rows, K, c.splits, kUnitK, c.tg, g) + 2 * ring1 > kSmemBudget) c.splits <<= 1;
+    c.depth = (kSmemBudget - stage_bytes(rows, K, c.splits, kUnitK, c.tg, g)) / ring1;
     if (c.depth > max_depth_for(c.tg)) c.depth = max_depth_for(c.tg);
     if (g_force_depth && g_force_depth < c.depth) c.depth = g_force_depth;
     // out-feature tiles per CTA: about one CTA per SM in a single wave
@@ -533,7 +580,8 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
     const int tok = 8 * c.tg;
     const int rows = a.tokens < tok ? a.tokens : tok;
-    p.ring_offset = kHeaderBytes + (int)(((size_t)rows * p.xs_stride * sizeof(__half) + 127) / 128 * 128);
+    p.xsum_offset = kHeaderBytes + xs_bytes(rows, a.K, c.splits, kUnitK);
+    p.ring_offset = p.xsum_offset + xsum_bytes(c.tg, a.K, c.splits, kUnitK, a.g);
     const int n_tiles = a.N / kTileN;
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;

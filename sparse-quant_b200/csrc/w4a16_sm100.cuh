@@ -49,12 +49,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // false on timeout or when another role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns)
 {
-    constexpr uint32_t kSuspendNs = 1000000;                 // 1 ms per probe
+    constexpr uint32_t kSuspendNs = 1000000;                 // hint: up to 1 ms per probe
     if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
     const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity, kSuspendNs)) {
-        if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > budget_ns) { *abort_flag = 1; return false; }
+        __nanosleep(128);                                    // leave the issue slots to the warps that have work
+        if ((++polls & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > budget_ns) { *abort_flag = 1; return false; }
+        }
     }
     return true;
 }

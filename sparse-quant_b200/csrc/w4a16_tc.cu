@@ -38,7 +38,7 @@ namespace {
 
 constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 packed tiles)
 constexpr int kBlockK   = 64;                  // k per stage (2 packed tiles)
-constexpr int kThreads  = 192;
+constexpr int kThreads  = 320;                 // warps 0-3, 6-9: dequantisers; warp 4: TMA; warp 5: MMA
 constexpr int kTmemCols = 512;
 constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;   // 0.4 s: far above any legitimate wait
 
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(dfull_bar, 1);
-        mbar_init(dempty_bar, 4);
+        mbar_init(dempty_bar, 8);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -167,22 +167,32 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             }
         }
     } else {
-        // ------------------------------ dequant + epilogue (warps 0..3) ------------------------------
+        // ------------------------------ dequant + epilogue (warps 0..3 and 6..9) ------------------------------
+        // Two groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which is
+        // also the packed tile column it dequantises.  Group 0 takes the even k-steps, group 1 the odd ones
+        // (counted across tiles, so the alternation follows the stage ring); each group drains half of the
+        // accumulator columns in the epilogue.
         int stage = 0; uint32_t phase = 0, dphase = 0;
         bool ok = true;
         const int r = lane >> 2;
-        const uint32_t lane_field = (uint32_t)(warp * 32) << 16;
+        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : 1;
+        uint32_t step_parity = 0;
+        const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
-            const bool has_tile = nb * 4 + warp < n_tiles;
-            for (int ks = 0; ks < k_steps; ++ks) {
+            const bool has_tile = nb * 4 + quarter < n_tiles;
+            for (int ks = 0; ks < k_steps; ++ks, step_parity ^= 1u) {
+                if (step_parity != (uint32_t)dgroup) {                 // the other group's stage
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                    continue;
+                }
                 ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs));
                 if (!ok) break;
                 if (has_tile) {
                     const unsigned char* st = smem + stage * Cfg::kStageBytes;
                     const uint4* wq = reinterpret_cast<const uint4*>(st + Cfg::kXBytes);
-                    const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + warp * 32 + r;
-                    const uint4 q0 = wq[warp * 32 + lane], q1 = wq[128 + warp * 32 + lane];
+                    const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + quarter * 32 + r;
+                    const uint4 q0 = wq[quarter * 32 + lane], q1 = wq[128 + quarter * 32 + lane];
                     const uint32_t words[2][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}};
 #pragma unroll
                     for (int nh = 0; nh < 2; ++nh) {
@@ -218,12 +228,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             if (!ok) break;
             dphase ^= 1u;
             tc_fence_after_sync();
-            const int n = nb * kBlockN + warp * 32 + lane;
+            const int n = nb * kBlockN + quarter * 32 + lane;
             const bool n_ok = n < p.N;
             const __half bias = (p.bias && n_ok) ? p.bias[n] : __half();
             const int tok0 = tb * TOK;
 #pragma unroll 1
-            for (int c0 = 0; c0 < TOK; c0 += 32) {
+            for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
                 tmem_wait_ld();
