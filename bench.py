@@ -555,17 +555,20 @@ def prefill_sweep(lib, weights, dev, stream, sets, peaks):
         for M in PREFILL_M:
             x = torch.randn(M, K, device=dev, dtype=torch.float16)
             o = torch.empty(M, N, device=dev, dtype=torch.float16)
+            ws_bytes = lib.w4a16_workspace_bytes(M, N, K, G)          # > 0 when the library wants to split K
+            ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
 
-            def fn(i, M=M, K=K, N=N, x=x, o=o):
+            def fn(i, M=M, K=K, N=N, x=x, o=o, ws=ws, ws_bytes=ws_bytes):
                 qw, zs = weights[(K, N)][i % sets]
-                r = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G, None, 0, sp)
+                r = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G,
+                                   ws.data_ptr() if ws_bytes else None, ws_bytes, sp)
                 if r != 0:
                     raise RuntimeError(lib.w4a16_status_str(r).decode())
             ms = time_calls(fn, stream, 20, warm=3)
             tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
             rows.append({"K": K, "N": N, "M": M, "ms": ms, "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
-                         "frac_of_nominal_2250": tf / 2250.0})
-            del x, o
+                         "frac_of_nominal_2250": tf / 2250.0, "workspace_bytes": ws_bytes})
+            del x, o, ws
     flag = ctypes.c_int(0)
     lib.w4a16_device_error_flag(ctypes.byref(flag))
     return {"rows": rows, "kernel": "tc_kernel (TMA + tcgen05.mma, A from TMEM)", "timeout_flag": flag.value,

@@ -136,7 +136,10 @@ int encode_tensor_map_2d(void* tmap, const void* base, int elem_bytes, const uin
                          const uint32_t box[2], bool swizzle128);                       // per-device word a kernel sets to 1 when a bounded wait gives up
 
 int launch_skinny(const GemmArgs& a, cudaStream_t st);
-int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+// err_word: device word raised on a barrier timeout (nullptr = the library's per-device word)
+// force_split: 0 = planned, otherwise the number of K parts per output tile
+int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st, int* err_word = nullptr,
+              int force_split = 0);
 size_t tc_workspace_bytes(int tokens, int N, int K, int g);
 bool tc_supported(int tokens, int N, int K, int g);
 

@@ -40,16 +40,23 @@ constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 p
 constexpr int kBlockK   = 64;                  // k per stage (2 packed tiles)
 constexpr int kThreads  = 320;                 // warps 0-3, 6-9: dequantisers; warp 4: TMA; warp 5: MMA
 constexpr int kTmemCols = 512;
+#ifndef W4A16_TC_STAGES_256
+#define W4A16_TC_STAGES_256 6
+#endif
 constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;   // 0.4 s: far above any legitimate wait
 
 template <int TOK>
 struct TcCfg {
-    static constexpr int kStages   = TOK == 256 ? 4 : (TOK == 128 ? 6 : 9);   // > 113 KB each: one CTA per SM
+    // as many stages as shared memory (227 KB) and the TMEM A ring allow: the pipeline is latency-bound when few
+    // tiles share the machine, so bytes in flight per SM matter (all variants exceed 113 KB: one CTA per SM)
+    static constexpr int kStages   = TOK == 256 ? W4A16_TC_STAGES_256 : (TOK == 128 ? 10 : 14);
     static constexpr int kXBytes   = TOK * kBlockK * 2;
     static constexpr int kWBytes   = 2 * 4 * 512;
     static constexpr int kStageBytes = kXBytes + kWBytes + 1024;     // zs padded to keep 1024-B alignment
     static constexpr int kACol     = TOK;                             // first TMEM column of the A ring
-    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/;
+    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 512 /*barriers*/;
+    static_assert(8 * (3 * kStages + 3) + 12 <= 512, "barrier area");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
     static_assert(kACol + 32 * kStages <= kTmemCols, "TMEM budget");
 };
 
@@ -61,6 +68,9 @@ struct TcParams {
     int*            error;          // device word, set non-zero on a wait timeout
     int tokens, N, K, g;
     int n_blocks, t_blocks;
+    int split;                      // K parts per output tile (1 = no split)
+    float* partial;                 // split > 1: fp32 partial tiles [split][tokens][N]
+    int*   counters;                // split > 1: arrivals per output tile (zero on entry, reset by the last arriver)
 };
 
 template <int TOK>
@@ -73,13 +83,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + S * Cfg::kStageBytes;
-    // barrier layout (8 B each): full[S], afull[S], empty[S], dfull, dempty ; then tmem ptr, abort flag
+    // barrier layout (8 B each): full[S], afull[S], empty[S], dfull, dempty, epi ; then tmem ptr, abort flag, last flag
     auto full_bar  = [&](int s) { return bar_base + 8u * s; };
     auto afull_bar = [&](int s) { return bar_base + 8u * (S + s); };
     auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-    const uint32_t dfull_bar = bar_base + 8u * (3 * S), dempty_bar = bar_base + 8u * (3 * S + 1);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S * Cfg::kStageBytes + 8 * (3 * S + 2));
+    const uint32_t dfull_bar = bar_base + 8u * (3 * S), dempty_bar = bar_base + 8u * (3 * S + 1), epi_bar = bar_base + 8u * (3 * S + 2);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S * Cfg::kStageBytes + 8 * (3 * S + 3));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -91,6 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
         mbar_init(dfull_bar, 1);
         mbar_init(dempty_bar, 8);
+        mbar_init(epi_bar, 8);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -106,17 +118,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
     const int n_tiles = p.N / kTileN;
     const int k_steps = p.K / kBlockK;
-    const int total_tiles = p.n_blocks * p.t_blocks;
+    const int total_tiles = p.n_blocks * p.t_blocks * p.split;      // work items: (output tile, K part)
+    auto k_range = [&](int item, int& ks0, int& ks1) {
+        const int kp = item % p.split;
+        ks0 = (int)((long long)k_steps * kp / p.split);
+        ks1 = (int)((long long)k_steps * (kp + 1) / p.split);
+    };
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const int tile = item / p.split;
                 const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
                 const int nb_tiles = min(4, n_tiles - nb * 4);
-                for (int ks = 0; ks < k_steps; ++ks) {
+                int ks0, ks1;
+                k_range(item, ks0, ks1);
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
                     const uint32_t st = smem_base + stage * Cfg::kStageBytes;
@@ -144,11 +164,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             constexpr uint32_t idesc = idesc_f16_m128(TOK);
             int stage = 0; uint32_t phase = 0, dphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 ok = mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs);   // epilogue drained D
                 if (!ok) break;
                 tc_fence_after_sync();
-                for (int ks = 0; ks < k_steps; ++ks) {
+                int ks0, ks1;
+                k_range(item, ks0, ks1);
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs) &&
                          mbar_wait(afull_bar(stage), phase, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
@@ -157,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                     const uint32_t a_tmem = tmem_base + Cfg::kACol + 32 * stage;
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
-                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
                     tc_commit(empty_bar(stage));
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
@@ -176,12 +198,23 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         bool ok = true;
         const int r = lane >> 2;
         const int quarter = warp & 3, dgroup = warp < 4 ? 0 : 1;
-        uint32_t step_parity = 0;
+        uint32_t step_parity = 0, epi_phase = 0;
+        // bounded rendezvous of the eight dequant/epilogue warps (split-K finalisation)
+        auto epi_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_bar);
+            const bool done = __all_sync(0xffffffffu, mbar_wait(epi_bar, epi_phase, abort_flag, kWaitBudgetNs));
+            epi_phase ^= 1u;
+            return done;
+        };
         const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            const int tile = item / p.split, kp = item % p.split;
             const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
             const bool has_tile = nb * 4 + quarter < n_tiles;
-            for (int ks = 0; ks < k_steps; ++ks, step_parity ^= 1u) {
+            int ks0, ks1;
+            k_range(item, ks0, ks1);
+            for (int ks = ks0; ks < ks1; ++ks, step_parity ^= 1u) {
                 if (step_parity != (uint32_t)dgroup) {                 // the other group's stage
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                     continue;
@@ -232,22 +265,76 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             const bool n_ok = n < p.N;
             const __half bias = (p.bias && n_ok) ? p.bias[n] : __half();
             const int tok0 = tb * TOK;
+            if (p.split == 1) {
 #pragma unroll 1
-            for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
-                tmem_wait_ld();
-                if (n_ok) {
+                for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
+                    tmem_wait_ld();
+                    if (n_ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int t = tok0 + c0 + j;
-                        if (t < p.tokens) {
-                            __half h = __float2half_rn(__uint_as_float(v[j]));
-                            if (p.bias) h = __hadd(h, bias);
-                            p.out[(size_t)t * p.N + n] = h;
+                        for (int j = 0; j < 32; ++j) {
+                            const int t = tok0 + c0 + j;
+                            if (t < p.tokens) {
+                                __half h = __float2half_rn(__uint_as_float(v[j]));
+                                if (p.bias) h = __hadd(h, bias);
+                                p.out[(size_t)t * p.N + n] = h;
+                            }
                         }
                     }
                 }
+            } else {
+                // split-K: park the fp32 partial tile in the workspace; the CTA that completes the tile (the last
+                // of `split` arrivals, found with one atomic per CTA) adds the parts in a fixed order - deterministic.
+                float* mine = p.partial + (size_t)kp * p.tokens * p.N;
+#pragma unroll 1
+                for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
+                    tmem_wait_ld();
+                    if (n_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int t = tok0 + c0 + j;
+                            if (t < p.tokens) mine[(size_t)t * p.N + n] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+                __threadfence();
+                if (!(ok = epi_sync())) break;                               // every warp's part of the tile is in the workspace
+                if (warp == 0 && lane == 0) {
+                    const int old = atomicAdd(p.counters + tile, 1);
+                    const int last = old == p.split - 1;
+                    if (last) p.counters[tile] = 0;                          // ready for the next launch
+                    *last_flag = last;
+                }
+                if (!(ok = epi_sync())) break;
+                if (*last_flag) {
+                    __threadfence();
+                    if (n_ok) {
+#pragma unroll 1
+                        for (int c = dgroup * (TOK / 2); c < (dgroup + 1) * (TOK / 2); c += 8) {
+                            float v[4][8];                                   // up to 4 parts x 8 tokens in flight
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const int t = tok0 + c + j;
+                                    v[q][j] = (q < p.split && t < p.tokens) ? __ldcg(p.partial + ((size_t)q * p.tokens + t) * p.N + n) : 0.f;
+                                }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int t = tok0 + c + j;
+                                if (t < p.tokens) {
+                                    __half h = __float2half_rn(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j]);
+                                    if (p.bias) h = __hadd(h, bias);
+                                    p.out[(size_t)t * p.N + n] = h;
+                                }
+                            }
+                        }
+                    }
+                }
+                if (!(ok = epi_sync())) break;                               // last_flag may be rewritten by the next item
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -300,25 +387,42 @@ __global__ void __launch_bounds__(128, 1) tmem_layout_probe_kernel(uint32_t* out
     if (warp == 0) tmem_dealloc(base, 32);
 }
 
-int g_force_tok = 0;
+int g_force_tok = 0, g_force_split = 0;
 
-int pick_tok(int tokens, int N, int K)
+struct TcPlan { int tok, split; };
+
+// Token tile and K split by a cost model in SM clocks: waves of work items x (k-steps x max(MMA, dequant) +
+// epilogue) plus, for split-K, the round trip of the fp32 partial tiles through L2.
+TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0)
 {
-    if (g_force_tok == 64 || g_force_tok == 128 || g_force_tok == 256) return g_force_tok;
     const int n_blocks = (N + kBlockN - 1) / kBlockN;
     const long long k_steps = K / kBlockK;
-    int best = 256;
-    long long best_cost = -1;
+    TcPlan best = {256, 1};
+    double best_cost = -1;
     const int cands[3] = {256, 128, 64};
     for (int i = 0; i < 3; ++i) {
         const int t = cands[i];
-        const long long tiles = (long long)n_blocks * ((tokens + t - 1) / t);
-        const long long waves = (tiles + 147) / 148;
-        const long long step = 2 * t > 240 ? 2 * t : 240;            // clocks: MMA vs dequant bound
-        const long long cost = waves * (k_steps * step + 6 * t + 2000);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = t; }
+        if (g_force_tok && t != g_force_tok) continue;
+        for (int sp = 1; sp <= 4; sp *= 2) {
+            if (g_force_split && !force_split ? sp != g_force_split : (sp > 1 && !allow_split)) continue;
+            if (sp > 1 && k_steps / sp < 8) continue;
+            // measured: splitting only pays when K is long and the unsplit tiles leave most SMs idle
+            if (sp > 1 && !g_force_split && !force_split && (K < 8192 || sp != 2 || (long long)n_blocks * ((tokens + t - 1) / t) * 2 > 148)) continue;
+            if (force_split && sp != force_split) continue;
+            const long long items = (long long)n_blocks * ((tokens + t - 1) / t) * sp;
+            const long long waves = (items + 147) / 148;
+            const double step = 2.0 * t > 240 ? 2.0 * t : 240;                       // MMA vs dequant bound
+            double cost = waves * ((double)(k_steps / sp) * step + 6.0 * t + 2000);
+            if (sp > 1) cost += (double)sp * tokens * N * 8.0 / 3000.0 + 3000;       // partials written + read back (~3 KB/clk)
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {t, sp}; }
+        }
     }
     return best;
+}
+
+size_t split_workspace_bytes(int tokens, int N, int split, int tiles)
+{
+    return (size_t)split * tokens * N * sizeof(float) + (((size_t)tiles * sizeof(int) + 255) / 256) * 256;
 }
 
 template <int TOK>
@@ -341,20 +445,29 @@ int launch_tok(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t
 
 }  // namespace
 
-void tc_force_config(int tile_tokens, int /*split_k*/) { g_force_tok = tile_tokens; }
+void tc_force_config(int tile_tokens, int split_k) { g_force_tok = tile_tokens; g_force_split = split_k; }
 
 bool tc_supported(int tokens, int N, int K, int g)
 {
     return tokens > 0 && (g == 64 || g == 128) && (K % kBlockK) == 0 && (N % kTileN) == 0;
 }
 
-size_t tc_workspace_bytes(int, int, int, int) { return 0; }
-
-int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
+size_t tc_workspace_bytes(int tokens, int N, int K, int g)
 {
-    int* err = device_error_word();
+    if (!tc_supported(tokens, N, K, g)) return 0;
+    const TcPlan pl = pick_plan(tokens, N, K, true);
+    if (pl.split == 1) return 0;
+    const int tiles = ((N + kBlockN - 1) / kBlockN) * ((tokens + pl.tok - 1) / pl.tok);
+    return split_workspace_bytes(tokens, N, pl.split, tiles);
+}
+
+int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st, int* err_word, int force_split)
+{
+    int* err = err_word ? err_word : device_error_word();
     if (!err) return W4A16_ERR_CUDA;
-    const int tok = pick_tok(a.tokens, a.N, a.K);
+    // split-K needs the caller's workspace; without one the best unsplit plan is used
+    TcPlan pl = pick_plan(a.tokens, a.N, a.K, workspace != nullptr, force_split);
+    const int tok = pl.tok;
 
     CUtensorMap map;
     {
@@ -370,6 +483,16 @@ int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
     p.n_blocks = (a.N + kBlockN - 1) / kBlockN;
     p.t_blocks = (a.tokens + tok - 1) / tok;
     const long long tiles = (long long)p.n_blocks * p.t_blocks;
+    p.split = pl.split; p.partial = nullptr; p.counters = nullptr;
+    if (pl.split > 1) {
+        const size_t need = split_workspace_bytes(a.tokens, a.N, pl.split, (int)tiles);
+        if (!workspace || workspace_bytes < need) return W4A16_ERR_WORKSPACE;
+        if (((uintptr_t)workspace & 255)) return W4A16_ERR_MISALIGNED;
+        p.partial = reinterpret_cast<float*>(workspace);
+        p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + (size_t)pl.split * a.tokens * a.N * sizeof(float));
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, (size_t)tiles * sizeof(int), st);   // arrival counters start at zero
+        if (e != cudaSuccess) return record_cuda_error(e);
+    }
     int sms = 148;
     {
         static int cached[64] = {0};
@@ -379,7 +502,8 @@ int launch_tc(const GemmArgs& a, void*, size_t, cudaStream_t st)
             if (cached[dev] > 0) sms = cached[dev];
         }
     }
-    const int grid = (int)(tiles < sms ? tiles : sms);
+    const long long items = tiles * pl.split;
+    const int grid = (int)(items < sms ? items : sms);
     switch (tok) {
         case 256: return launch_tok<256>(map, p, grid, st);
         case 128: return launch_tok<128>(map, p, grid, st);

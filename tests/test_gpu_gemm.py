@@ -107,6 +107,29 @@ def test_tc_every_token_tile(tile):
         lib.w4a16_tune_tc(0, 0)
 
 
+@pytest.mark.parametrize("tile,split", [(256, 2), (128, 2), (128, 4), (64, 4)])
+def test_tc_split_k(tile, split):
+    """K split over several CTAs per output tile: fp32 partials through the workspace, summed in a fixed
+    order by the last arriver - parity, determinism, counters left at zero for the next call."""
+    import quant
+    lib = quant.load_library()
+    try:
+        lib.w4a16_tune_tc(tile, split)
+        for _ in range(2):                                   # second call reuses self-reset counters
+            run(300, 384, 2048, 128, algo=2, bias=True)
+        run(70, 1376, 1408, 64, algo=2)
+        p = packed(384, 2048, 128)
+        qw, zs = to_dev(p)
+        x = make_x(300, 2048).cuda()
+        a = quant.gemm_awq_bias(x, qw, zs, None, 384, 128, algo=2)
+        b = quant.gemm_awq_bias(x, qw, zs, None, 384, 128, algo=2)
+        assert torch.equal(a, b)
+    finally:
+        lib.w4a16_tune_tc(0, 0)
+    flag = __import__("ctypes").c_int(-1)
+    assert lib.w4a16_device_error_flag(flag) == 0 and flag.value == 0
+
+
 def test_tc_bert_ffn_up_config():
     """BASELINE config 1: M=512 (4 x 128), K=1024, N=4096, g=128."""
     run(512, 4096, 1024, 128, algo=0, bias=True)
