@@ -140,6 +140,24 @@ int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_d
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * No counterpart in the reference.  The tcgen05 GEMM with K split in two, for callers that cannot
+ * allocate device memory (inside stream capture, inside a host runtime that owns the allocator, or
+ * with a memory budget pinned at start-up): the fp32 partial tiles, the arrival counters and the
+ * error word live in a file-scope device array of the library (about 16 MiB per GPU that loads the
+ * library, held until the process exits).  Nothing is allocated or freed, no workspace argument.
+ * Limits: 2 * tokens * N * 4 bytes <= 16 MiB and at most 4096 output tiles, K >= 1024, g in {64, 128};
+ * beyond that W4A16_ERR_TOO_LARGE / W4A16_ERR_BAD_SHAPE.  All calls on a device share the array:
+ * calls whose kernels could overlap on the GPU (different streams) must be serialised by the caller.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and clears
+ * the error word on `stream`: make that first call outside stream capture.
+ */
+int w4a16_gemm_static_scratch(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                              void* out, int tokens, int N, int K, int group_size, void* stream);
+
+/* Error word of w4a16_gemm_static_scratch on the current device (see w4a16_device_error_flag). */
+int w4a16_static_scratch_error_flag(int* flag);
+
+/*
  * Both GEMM kernels bound every barrier wait; if one ever times out the kernel sets a
  * per-device error word, releases what it holds (tensor memory) and returns.  This reads that
  * word (*flag = 0: no kernel on the current device ever gave up).  Synchronises the device; the

@@ -513,6 +513,81 @@ int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaSt
 
 }  // namespace w4a16
 
+// ---------------------------------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at all: code running between cudaStreamBeginCapture and
+// EndCapture, plug-ins living inside another runtime's memory pool that forbids side allocations, and services
+// that pin their whole memory budget at start-up.  The split-K flavour of the tcgen05 kernel needs global scratch
+// (fp32 partial tiles, arrival counters) and every GEMM kernel needs an error word; here all three live in ONE
+// file-scope device array that is part of the loaded library image: every GPU that loads the library carries
+// these kStaticScratchBytes until the process exits, and nothing is ever allocated or freed.
+//   * capacity: 2 K parts x tokens x N fp32 <= kStaticPartialBytes (16 MiB, e.g. 512 x 4096) and at most
+//     kStaticMaxTiles output tiles; larger problems are refused with W4A16_ERR_TOO_LARGE;
+//   * all calls on a device share the array and it keeps the previous call's contents: the counters are cleared
+//     at the start of every call, the partial tiles are fully rewritten before they are read, and two calls whose
+//     kernels overlap on the GPU (different streams) race on it - serialise them;
+//   * in host code the array's name is only a handle: the device address comes from cudaGetSymbolAddress, looked
+//     up once per device (with that device current) by the first call on that device.  Make that first call
+//     outside stream capture.
+constexpr size_t kStaticPartialBytes = 16u << 20;
+constexpr int    kStaticMaxTiles     = 4096;
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticMaxTiles * sizeof(int) + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+extern "C" int w4a16_gemm_static_scratch(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                         void* out, int tokens, int N, int K, int group_size, void* stream)
+{
+    using namespace w4a16;
+    if (group_size != 64 && group_size != 128) return W4A16_ERR_GROUP_SIZE;
+    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || K < 1024) return W4A16_ERR_BAD_SHAPE;
+    if (!x || !qweight || !zeros_scales || !out) return W4A16_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 15) || ((uintptr_t)qweight & 15) || ((uintptr_t)zeros_scales & 15) || ((uintptr_t)out & 15))
+        return W4A16_ERR_MISALIGNED;
+    if ((size_t)2 * tokens * N * sizeof(float) > kStaticPartialBytes) return W4A16_ERR_TOO_LARGE;
+    if ((long long)((N + kBlockN - 1) / kBlockN) * ((tokens + 63) / 64) > kStaticMaxTiles) return W4A16_ERR_TOO_LARGE;
+
+    // once per device: resolve the device address of the file-scope array (the host-side name is not an address)
+    static unsigned char* base[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64) return W4A16_ERR_UNSUPPORTED_GPU;
+    if (!base[dev]) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (major != 10) return W4A16_ERR_UNSUPPORTED_GPU;
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) return record_cuda_error(e == cudaSuccess ? cudaErrorInvalidSymbol : e);
+        e = cudaMemsetAsync(ptr + kStaticScratchBytes - 256, 0, 256, (cudaStream_t)stream);     // error word starts clear
+        if (e != cudaSuccess) return record_cuda_error(e);
+        base[dev] = ptr;
+    }
+    unsigned char* scratch = base[dev];
+    int* err_word = reinterpret_cast<int*>(scratch + kStaticScratchBytes - 256);
+
+    GemmArgs a;
+    a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
+    a.bias = (const __half*)bias; a.out = (__half*)out;
+    a.tokens = tokens; a.N = N; a.K = K; a.g = group_size; a.static_weights = false;
+    // workspace handed to the kernel = the static array minus the error word; launch_tc clears the counters
+    return launch_tc(a, scratch, kStaticScratchBytes - 256, (cudaStream_t)stream, err_word, /*force_split=*/2);
+}
+
+// Reads the error word of the static-scratch entry point on the current device (0 = no barrier wait ever timed
+// out there; also 0 if the entry point was never used on this device).  Synchronises the device.
+extern "C" int w4a16_static_scratch_error_flag(int* flag)
+{
+    if (!flag) return W4A16_ERR_NULL_POINTER;
+    unsigned char* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess) return w4a16::record_cuda_error(e);
+    e = cudaMemcpy(flag, ptr + kStaticScratchBytes - 256, sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? W4A16_OK : w4a16::record_cuda_error(e);
+}
+
 // Debug aid: fills out[128][32] (device, uint32) with the tags read back by the probe kernel above.
 extern "C" int w4a16_debug_tmem_layout(void* out, void* stream)
 {

@@ -39,6 +39,8 @@ C_ABI = {
     "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
     "w4a16_gemm_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
     "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
+    "w4a16_gemm_static_scratch": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp]),
+    "w4a16_static_scratch_error_flag": (_ci, [ctypes.POINTER(_ci)]),
     "w4a16_dequant": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "w4a16_transpose_merge_zeros_scales": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "w4a16_convert_ours_to_awq": (_ci, [_vp, _vp, _ci, _ci, _vp]),
