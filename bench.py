@@ -204,7 +204,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--small", action="store_true", help="one weight set, no extras (for profiler captures)")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
-                    help="capture the step in a CUDA graph (auto: on for 1 GPU, off when NCCL collectives are in the step)")
+                    help="capture the step in a CUDA graph (auto: on unless NCCL collectives are in the step)")
+    ap.add_argument("--reduce", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how row-parallel outputs are summed - inside the decode kernel through peer memory, or by an NCCL all-reduce")
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
     ap.add_argument("--workload", default="decode-sweep", choices=["decode-sweep", "opt-6.7b", "llama2-7b"],
                     help="decode-sweep (default, the headline metric) or a full random-init W4A16 decoder stack: prefill + greedy decode tokens/s")
@@ -249,14 +251,21 @@ def main():
 
     # Tensor-parallel sharding of the sweep at N > 1 (Megatron style, as the model builder does it):
     #   4096 x 4096  (q/k/v-type) and 4096 x 16384 (fc1): column-parallel, each rank owns N / world out-features;
-    #   16384 x 4096 (fc2): row-parallel, each rank owns K / world in-features and the [M, 4096] fp16 partial
-    #   outputs are summed with one NCCL all-reduce per call.  Total work is fixed: strong scaling.
+    #   16384 x 4096 (fc2): row-parallel, each rank owns K / world in-features and the [M, 4096] partial outputs
+    #   are summed inside the kernel through peer memory (--reduce fused) or by one NCCL fp16 all-reduce per call.
+    #   Total work is fixed: strong scaling.
     def local_shape(K, N):
         if world == 1:
             return K, N, False
         if K > N:
             return K // world, N, True            # row-parallel -> all-reduce
         return K, N // world, False               # column-parallel
+
+    exchange = None
+    if world > 1 and args.reduce == "fused":
+        from w4a16.tp import PeerExchange
+        exchange = PeerExchange(max(DECODE_M) * max(N for _, N in DECODE_SHAPES), device=dev)
+        note("peer exchange buffers mapped")
 
     weights = {}
     for si, (K, N) in enumerate(DECODE_SHAPES):
@@ -274,11 +283,15 @@ def main():
         kl, nl, reduce = local_shape(K, N)
         # the packed weights are static module state: W4A16_FLAG_STATIC_WEIGHTS lets a launch prefetch them while
         # the previous kernel of the stream drains (x and out still wait for it)
-        r = lib.w4a16_gemm_ex(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
-                              M, nl, kl, G, None, 0, st, 0, 1)
+        if reduce and exchange is not None:
+            r = lib.w4a16_gemm_allreduce(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
+                                         M, nl, kl, G, kl, exchange.buffers, world, rank, exchange.capacity, st, 1)
+        else:
+            r = lib.w4a16_gemm_ex(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
+                                  M, nl, kl, G, None, 0, st, 0, 1)
         if r != 0:
             raise RuntimeError(lib.w4a16_status_str(r).decode())
-        if reduce:
+        if reduce and exchange is None:
             dist.all_reduce(outs[(M, K, N)])
 
     calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
@@ -292,7 +305,14 @@ def main():
             launch(*c, sp)
     stream.synchronize()
     note("eager pass done")
-    use_graph = args.graph == "on" or (args.graph == "auto" and world == 1)
+
+    def check_exchange(where):
+        if exchange is not None:
+            epoch, err = exchange.status()
+            if err:
+                raise RuntimeError(f"peer exchange gave up waiting for rank {err - 1} ({where}, after {epoch} calls)")
+    check_exchange("eager pass")
+    use_graph = args.graph == "on" or (args.graph == "auto" and (world == 1 or exchange is not None))
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
@@ -316,6 +336,7 @@ def main():
         for _ in range(args.warmup):
             run_step()
     barrier()
+    check_exchange("warm-up")
     note("warm-up done")
     sampler = ClockSampler(local)
     sampler.start()
@@ -327,6 +348,7 @@ def main():
             run_step()
         e1.record(stream)
     barrier()
+    check_exchange("timed region")
     note("timed region done")
     t1 = time.perf_counter()
     clocks = sampler.finish(t0, t1)
@@ -348,7 +370,9 @@ def main():
                    "timing": ("CUDA graph of one step, K replays between CUDA events on the launching stream" if use_graph else
                               "stream-ordered launches (no graph), K steps between CUDA events on the launching stream"),
                    "multi_gpu": (f"tensor parallel over {world} ranks: column-parallel 4096x4096 and 4096x16384, row-parallel "
-                                 f"16384x4096 with {collectives_per_step} NCCL fp16 all-reduces of [M,4096] per step") if world > 1 else "single GPU"},
+                                 f"16384x4096 with {collectives_per_step} sums of [M,4096] per step, " +
+                                 ("done inside the decode kernel: fp32 partials pushed over NVLink into every rank's exchange buffer, flag hand-shake per CTA"
+                                  if exchange is not None else "NCCL fp16 all-reduce after the kernel")) if world > 1 else "single GPU"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
@@ -395,10 +419,16 @@ def run_model(args):
         cfg, batch, prompt, new = DecoderConfig.llama2_7b(), 32, 1024, 256
     if args.layers:
         cfg.layers = args.layers
-    model = Decoder(cfg, rank, world, None, dev, seed=1234).mark_static()
+    exchange = None
+    if world > 1 and args.reduce == "fused":
+        from w4a16.tp import PeerExchange
+        exchange = PeerExchange(32 * cfg.hidden, device=dev)
+    model = Decoder(cfg, rank, world, None, dev, seed=1234, exchange=exchange).mark_static()
     ids = torch.randint(0, cfg.vocab, (batch, prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(7))
     steps, warm = max(1, min(args.steps, 5)), 1
-    graphed = world == 1          # NCCL collectives inside graph capture hung on this pool: eager steps for TP > 1
+    # NCCL collectives inside graph capture hung on this pool: with --reduce nccl the TP > 1 token steps run eagerly;
+    # with the fused exchange the step holds no library collective and is captured at any world size
+    graphed = (world == 1 or (exchange is not None and batch <= 32)) and args.graph != "off"
     gen = (lambda n: model.generate_graphed(ids, n, use_graph=True)) if graphed else (lambda n: model.generate_graphed(ids, n, use_graph=False))
     for _ in range(warm):
         gen(8)
@@ -411,6 +441,8 @@ def run_model(args):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         tp.append(float(t[0])); td.append(float(t[1]))
+        if exchange is not None and exchange.status()[1]:
+            raise RuntimeError(f"peer exchange gave up waiting for rank {exchange.status()[1] - 1}")
     prefill_tps = batch * prompt / float(np.mean(tp))
     decode_tps = batch * (new - 1) / float(np.mean(td))
     if world > 1:
@@ -425,6 +457,7 @@ def run_model(args):
                        "batch": batch, "prompt_tokens": prompt, "new_tokens": new, "parallelism": f"tp{world}",
                        "attention": "torch scaled_dot_product_attention over a static KV cache (not part of the W4A16 path)",
                        "decode_loop": "one CUDA graph per token step, replayed" if graphed else "eager token steps",
+                       "row_parallel_sum": "single GPU" if world == 1 else ("inside the decode kernel through peer memory" if exchange is not None and batch <= 32 else "NCCL fp16 all-reduce"),
                        "timing": "host wall clock around synchronised prefill / decode phases, max over ranks"},
             "prefill_tokens_per_s": prefill_tps, "decode_ms_per_token": 1e3 * float(np.mean(td)) / (new - 1),
         }), flush=True)

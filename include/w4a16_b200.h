@@ -140,6 +140,41 @@ int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_d
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Decode GEMV fused with the all-reduce of a row-parallel linear (tensor parallelism; no counterpart in the
+ * reference, which is single-GPU: it stands where a sharded WALinear.forward, qlinear.py:58-72, would be followed
+ * by an all-reduce).  Rank `rank` of `world` (<= 8, one process per GPU, all GPUs peer-accessible) holds the K
+ * shard [K of this call] of the packed weight; every rank calls this with its own shard and the same tokens (<= 32),
+ * N, group_size, k_config (the largest K shard over the ranks: all ranks must launch the same shape) and bias
+ * (added once, after the sum).  out = fp16(sum over ranks of x_r W_r^T) + bias on EVERY rank, bit-identical across
+ * ranks; partial sums cross NVLink in fp32.
+ *
+ * Exchange buffers: each rank allocates one (w4a16_exchange_alloc; capacity_elems >= tokens * N of any call that
+ * uses it), exports a 64-byte handle (w4a16_exchange_export), the host program moves the handles between the
+ * processes, and each rank opens its peers' handles (w4a16_exchange_open).  `buffers[r]` is rank r's buffer as
+ * mapped in the calling process (own allocation at index `rank`).  Calls that use the same buffers must be issued
+ * in the same order on every rank and must not overlap on one GPU (use one stream).  A rank whose peers do not
+ * show up within 2 s gives up: the library's device error word (w4a16_device_error_flag) and the buffer's error
+ * field (w4a16_exchange_status) are set and the output of that call is undefined; the kernel still returns.
+ * Allocates nothing per call and contains no library collective, so a stream capture can record it.
+ */
+size_t w4a16_exchange_bytes(int world, size_t capacity_elems);
+int w4a16_exchange_alloc(int world, size_t capacity_elems, void** buffer);
+int w4a16_exchange_free(void* buffer);
+int w4a16_exchange_export(void* buffer, void* handle64);
+int w4a16_exchange_open(const void* handle64, void** peer_buffer);
+int w4a16_exchange_close(void* peer_buffer);
+int w4a16_exchange_status(const void* buffer, unsigned* epoch, int* error);
+/* All-gather of `words` 32-bit words per rank through the same buffers and protocol (one small kernel):
+ * out[r * words + i] = rank r's in[i].  For what a decode step exchanges besides the row-parallel sums, e.g. each
+ * rank's best logit of its vocabulary shard. */
+int w4a16_exchange_allgather(const void* in, void* out, int words, void* const* buffers, int world, int rank,
+                             size_t capacity_elems, void* stream);
+int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                         void* out, int tokens, int N, int K, int group_size, int k_config,
+                         void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
+                         unsigned flags);
+
+/*
  * No counterpart in the reference.  The tcgen05 GEMM with K split in two, for callers that cannot
  * allocate device memory (inside stream capture, inside a host runtime that owns the allocator, or
  * with a memory budget pinned at start-up): the fp32 partial tiles, the arrival counters and the

@@ -56,6 +56,21 @@ __device__ __forceinline__ void unpack_s4x8_fast(uint32_t w, uint32_t (&h)[4])
     asm("sub.f16x2 %0, %1, %2;" : "=r"(h[2]) : "r"(c), "r"(k960));
 }
 
+// Cheapest form, for kernels that rescale in fp32 afterwards: each nibble is only masked in place, which leaves a
+// subnormal fp16 bit pattern.  h[0], h[2] (rows r) hold q * 2^-24, h[1], h[3] (rows r+8) hold q * 2^-20; the tensor
+// core multiplies subnormal fp16 inputs exactly, so the fp32 accumulators carry exact multiples of q * x.
+constexpr float kDenormScaleLo = 16777216.f;     // 2^24, rows r
+constexpr float kDenormScaleHi = 1048576.f;      // 2^20, rows r + 8
+__device__ __forceinline__ void unpack_s4x8_denorm(uint32_t w, uint32_t (&h)[4])
+{
+    constexpr uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u;
+    const uint32_t top = w >> 8;
+    h[0] = w & kLo;
+    h[1] = w & kHi;
+    h[2] = top & kLo;
+    h[3] = top & kHi;
+}
+
 // (t - z) * s in fp16 with flush-to-zero, two lanes at a time: bit-exact with apply_Q
 // (common.h:210-225, the non-FMA branch).
 __device__ __forceinline__ uint32_t dequant_h2(uint32_t t, uint32_t zz, uint32_t ss)
@@ -118,6 +133,25 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
 // ---------------------------------------------------------------------------------------------
 // host-side plumbing shared by the translation units
 // ---------------------------------------------------------------------------------------------
+// Exchange buffer of one rank for the GEMV fused with its all-reduce (row-parallel linears): every rank owns one
+// such buffer and maps all its peers' buffers.  Layout:
+//   [ExchangeHeader, 256 B][flags: 2 halves x kExchangeMaxCtas x kExchangeMaxWorld u32][data: 2 halves x world x capacity fp32]
+constexpr int    kExchangeMaxWorld  = 8;
+constexpr int    kExchangeMaxCtas   = 256;
+constexpr size_t kExchangeFlagsOffset = 256;
+constexpr size_t kExchangeDataOffset  = kExchangeFlagsOffset + 2 * (size_t)kExchangeMaxCtas * kExchangeMaxWorld * 4;
+struct ExchangeHeader {
+    unsigned epoch;     // calls completed on this rank; selects the buffer half (epoch & 1) and the flag value (epoch + 1)
+    unsigned ticket;    // CTAs of the running call that are done; the last one advances `epoch`
+    int      error;     // set when a wait for a peer gave up
+};
+struct ExchangeArgs {
+    unsigned char* peer[kExchangeMaxWorld];   // device pointers to every rank's buffer (own included), by rank
+    int world, rank;
+    long long capacity;                        // fp32 elements per (half, source rank) slot
+    int k_config;                              // K all ranks agree on for choosing the launch shape (largest K shard)
+};
+
 struct GemmArgs {
     const __half*   x;
     const uint32_t* qw;
@@ -126,6 +160,7 @@ struct GemmArgs {
     __half*         out;
     int tokens, N, K, g;
     bool static_weights;   // W4A16_FLAG_STATIC_WEIGHTS
+    const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
 };
 
 int  record_cuda_error(cudaError_t e);          // returns W4A16_ERR_CUDA, remembers e

@@ -1,0 +1,207 @@
+// Peer-memory exchange buffers and the C-ABI entry point of the decode GEMV fused with its all-reduce.
+//
+// A row-parallel linear (out_proj / fc2 / o_proj / down_proj under tensor parallelism) multiplies its K shard and
+// then needs the sum over ranks.  For decode-sized inputs the sum is done inside the GEMV kernel: each CTA pushes
+// its fp32 partial outputs over NVLink into every rank's exchange buffer, raises a flag there, waits (bounded) for
+// the matching CTAs of the other ranks, and adds the `world` partials in rank order.  No NCCL call, nothing that a
+// stream capture cannot record; partials stay fp32 until the single final rounding.
+//
+// The buffers are ordinary device allocations shared through CUDA IPC: w4a16_exchange_alloc on every rank, the
+// 64-byte handles exchanged by the host program (any transport), w4a16_exchange_open on every peer handle.
+#include <cstring>
+
+#include "w4a16_common.cuh"
+
+using namespace w4a16;
+
+namespace {
+
+__device__ __forceinline__ unsigned long long timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+struct GatherParams {
+    unsigned char* peer[kExchangeMaxWorld];
+    unsigned char* self;
+    const unsigned* in;      // `words` 32-bit words of this rank
+    unsigned* out;           // [world][words]
+    int* error;
+    int words, world, rank;
+    long long capacity;
+};
+
+// All-gather of a few 32-bit words per rank through the exchange buffers (one CTA): push this rank's words into
+// slot [half][rank] of every rank's buffer, raise the flag of CTA 0 there, wait (bounded) for every rank's flag
+// here, copy the `world` slots out in rank order, advance the epoch.  Same protocol as the fused GEMV epilogue,
+// so the two can be mixed on one set of buffers.
+__global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherParams p)
+{
+    ExchangeHeader* hdr = reinterpret_cast<ExchangeHeader*>(p.self);
+    const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&hdr->epoch);
+    const unsigned half_sel = epoch & 1u, tag = epoch + 1u;
+    for (int i = threadIdx.x; i < p.words; i += blockDim.x) {
+        const unsigned v = p.in[i];
+        const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + i;
+#pragma unroll
+        for (int d = 0; d < kExchangeMaxWorld; ++d)
+            if (d < p.world) reinterpret_cast<unsigned*>(p.peer[d] + kExchangeDataOffset)[idx] = v;
+    }
+    __syncthreads();
+    const size_t fidx = (size_t)half_sel * kExchangeMaxCtas * kExchangeMaxWorld;       // flags of CTA 0
+    if ((int)threadIdx.x < p.world) {
+        unsigned char* dst = p.self;
+#pragma unroll
+        for (int d = 0; d < kExchangeMaxWorld; ++d)
+            if (d == (int)threadIdx.x) dst = p.peer[d];
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(dst + kExchangeFlagsOffset) + fidx + p.rank), "r"(tag) : "memory");
+        const unsigned* mine = reinterpret_cast<const unsigned*>(p.self + kExchangeFlagsOffset) + fidx + threadIdx.x;
+        const unsigned long long t0 = timer_ns();
+        unsigned polls = 0, seen = 0;
+        const bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;     // an earlier wait gave up: do not wait again
+        while (!dead) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (seen == tag) break;
+            if ((++polls & 255u) == 0 && timer_ns() - t0 > 2000000000ull) {
+                atomicExch(p.error, 2);
+                atomicExch(&hdr->error, 1 + (int)threadIdx.x);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const unsigned* data = reinterpret_cast<const unsigned*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+    for (int i = threadIdx.x; i < p.words * p.world; i += blockDim.x) {
+        const int src = i / p.words, w = i - src * p.words;
+        p.out[i] = __ldcg(data + (size_t)src * p.capacity + w);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned*>(&hdr->epoch) = epoch + 1;
+}
+
+}  // namespace
+
+extern "C" size_t w4a16_exchange_bytes(int world, size_t capacity_elems)
+{
+    if (world < 1 || world > kExchangeMaxWorld) return 0;
+    return kExchangeDataOffset + 2 * (size_t)world * capacity_elems * sizeof(float);
+}
+
+extern "C" int w4a16_exchange_alloc(int world, size_t capacity_elems, void** buffer)
+{
+    if (!buffer) return W4A16_ERR_NULL_POINTER;
+    const size_t bytes = w4a16_exchange_bytes(world, capacity_elems);
+    if (!bytes || !capacity_elems) return W4A16_ERR_BAD_SHAPE;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    e = cudaMemset(p, 0, bytes);                       // epoch 0, all flags 0: no call has happened yet
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { cudaFree(p); return record_cuda_error(e); }
+    *buffer = p;
+    return W4A16_OK;
+}
+
+extern "C" int w4a16_exchange_free(void* buffer)
+{
+    if (!buffer) return W4A16_OK;
+    cudaError_t e = cudaFree(buffer);
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
+extern "C" int w4a16_exchange_export(void* buffer, void* handle64)
+{
+    if (!buffer || !handle64) return W4A16_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, buffer);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    std::memcpy(handle64, &h, 64);
+    return W4A16_OK;
+}
+
+extern "C" int w4a16_exchange_open(const void* handle64, void** peer_buffer)
+{
+    if (!handle64 || !peer_buffer) return W4A16_ERR_NULL_POINTER;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    *peer_buffer = p;
+    return W4A16_OK;
+}
+
+extern "C" int w4a16_exchange_close(void* peer_buffer)
+{
+    if (!peer_buffer) return W4A16_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(peer_buffer);
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
+extern "C" int w4a16_exchange_status(const void* buffer, unsigned* epoch, int* error)
+{
+    if (!buffer) return W4A16_ERR_NULL_POINTER;
+    ExchangeHeader h;
+    cudaError_t e = cudaMemcpy(&h, buffer, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (epoch) *epoch = h.epoch;
+    if (error) *error = h.error;
+    return W4A16_OK;
+}
+
+extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                    void* out, int tokens, int N, int K, int group_size, int k_config,
+                                    void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
+                                    unsigned flags)
+{
+    if (group_size != 32 && group_size != 64 && group_size != 128) return W4A16_ERR_GROUP_SIZE;
+    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || k_config < K) return W4A16_ERR_BAD_SHAPE;
+    if (tokens > 32) return W4A16_ERR_TOO_LARGE;
+    if (!x || !qweight || !zeros_scales || !out || !buffers) return W4A16_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 15) || ((uintptr_t)qweight & 15) || ((uintptr_t)zeros_scales & 15) || ((uintptr_t)out & 15))
+        return W4A16_ERR_MISALIGNED;
+    if (world < 1 || world > kExchangeMaxWorld || rank < 0 || rank >= world) return W4A16_ERR_BAD_SHAPE;
+    if (flags & ~(unsigned)W4A16_FLAG_STATIC_WEIGHTS) return W4A16_ERR_BAD_ALGO;
+    int dev = 0, major = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (major != 10) return W4A16_ERR_UNSUPPORTED_GPU;
+
+    ExchangeArgs ex;
+    for (int d = 0; d < kExchangeMaxWorld; ++d) ex.peer[d] = d < world ? (unsigned char*)buffers[d] : nullptr;
+    ex.world = world; ex.rank = rank; ex.capacity = (long long)capacity_elems; ex.k_config = k_config;
+    GemmArgs a;
+    a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
+    a.bias = (const __half*)bias; a.out = (__half*)out;
+    a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
+    a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
+    a.exchange = &ex;
+    return launch_skinny(a, (cudaStream_t)stream);
+}
+
+extern "C" int w4a16_exchange_allgather(const void* in, void* out, int words, void* const* buffers, int world, int rank,
+                                        size_t capacity_elems, void* stream)
+{
+    if (!in || !out || !buffers) return W4A16_ERR_NULL_POINTER;
+    if (words <= 0 || world < 1 || world > kExchangeMaxWorld || rank < 0 || rank >= world) return W4A16_ERR_BAD_SHAPE;
+    if ((size_t)words > capacity_elems) return W4A16_ERR_TOO_LARGE;
+    GatherParams p;
+    for (int d = 0; d < kExchangeMaxWorld; ++d) {
+        p.peer[d] = d < world ? (unsigned char*)buffers[d] : nullptr;
+        if (d < world && !p.peer[d]) return W4A16_ERR_NULL_POINTER;
+    }
+    p.self = p.peer[rank];
+    p.in = (const unsigned*)in; p.out = (unsigned*)out;
+    p.error = device_error_word();
+    if (!p.error) return W4A16_ERR_CUDA;
+    p.words = words; p.world = world; p.rank = rank; p.capacity = (long long)capacity_elems;
+    exchange_allgather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}

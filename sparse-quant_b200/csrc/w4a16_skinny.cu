@@ -13,11 +13,13 @@
 //     512-byte tiles in one operation) plus one 128-byte bulk copy per quantisation group of its
 //     (zero, scale) pairs, all completing on the unit's own mbarrier - about 130 KB in flight per
 //     SM with no registers spent on it;
-//   * the nibbles are expanded in registers to fp16 (64 + q) - exact - and fed straight to
+//   * the nibbles are only masked in place (one shift + four ANDs per eight weights), which leaves subnormal
+//     fp16 patterns q * 2^-24 / q * 2^-20 that the tensor core multiplies exactly, and are fed straight to
 //     mma.m16n8k16 as the A fragment (the packed layout IS that fragment); activations are staged
-//     once per CTA in shared memory and read with ldmatrix as the B fragment; a second MMA with an
-//     all-ones A fragment yields sum_k x[t, k] of the group.  At the end of each quantisation group
-//     the zero point and the scale are applied in fp32:  acc += s * (sum (64+q) x - (64+z) sum x).
+//     once per CTA in shared memory and read with ldmatrix as the B fragment; sum_k x[t, k] of every
+//     group is computed once per CTA by an MMA with an all-ones A fragment.  At the end of each
+//     quantisation group the zero point and the scale are applied in fp32 (the power of two folded into
+//     both):  acc += s * (sum q x - z sum x).
 //     That is (q - z) * s without the intermediate fp16 rounding of the weight; with the identity
 //     matrix as input the output reproduces the reference's dequantised weight bit for bit
 //     (denormal scales are flushed to zero as mul.ftz does), and for general inputs it agrees with
@@ -79,6 +81,11 @@ struct SkinnyParams {
     int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
     int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
+    // fused all-reduce over peer memory (world == 0: plain store of this GPU's result)
+    unsigned char* peer[kExchangeMaxWorld];
+    unsigned char* self;          // = peer[rank]
+    int world, rank;
+    long long capacity;
     unsigned long long* timeline;   // debug: [cta][warp][8] globaltimer stamps, or null
     int debug_mode;  // experiments: bit 0 = skip the MMA work, bit 1 = skip staging the activations
 };
@@ -129,8 +136,8 @@ __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float 
                         a0[0] = a0[1] = a0[2] = a0[3] = words[kh * 2 + 0];
                         a1[0] = a1[1] = a1[2] = a1[3] = words[kh * 2 + 1];
                     } else {
-                        unpack_s4x8_fast(words[kh * 2 + 0], a0);
-                        unpack_s4x8_fast(words[kh * 2 + 1], a1);
+                        unpack_s4x8_denorm(words[kh * 2 + 0], a0);
+                        unpack_s4x8_denorm(words[kh * 2 + 1], a1);
                     }
 #pragma unroll
                     for (int tg = 0; tg < TG; ++tg) {
@@ -168,8 +175,11 @@ __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float 
                     uint32_t v = slot->zs[gi][nh * 16 + hi * 8 + r];
                     asm("mul.ftz.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(kOnes));
                     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
-                    zf[hi] = f.x;
-                    sf[hi] = f.y;
+                    // the accumulators hold sum(q x) * 2^-24 (rows r) or * 2^-20 (rows r+8): fold the power of two
+                    // into the zero point (zero = f.x - 64) and the scale; both products are exact in fp32
+                    const float up = hi ? kDenormScaleHi : kDenormScaleLo;
+                    zf[hi] = (f.x - 64.f) * (1.f / up);
+                    sf[hi] = f.y * up;
                 }
 #pragma unroll
                 for (int tg = 0; tg < TG; ++tg) {
@@ -182,6 +192,18 @@ __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float 
         }
     }
 }
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+constexpr uint64_t kPeerWaitBudgetNs = 2000ull * 1000 * 1000;     // a peer that does not show up within 2 s is given up on
 
 // fp32 load from the shared memory of CTA `rank` of this cluster (own rank included)
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank)
@@ -409,6 +431,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     if (S > 1) cluster.sync();                              // every rank's partial sums are in place
     if (tl) tl[6] = globaltimer_ns();
 
+    // fused all-reduce: the epoch is read after the main loop, i.e. after griddepcontrol.wait under programmatic
+    // launch - the previous call on this stream has advanced it by then
+    const bool fused = p.world > 0;
+    ExchangeHeader* hdr = reinterpret_cast<ExchangeHeader*>(p.self);
+    const unsigned epoch = fused ? *reinterpret_cast<volatile unsigned*>(&hdr->epoch) : 0u;
+    const unsigned half_sel = epoch & 1u, tag = epoch + 1u;
+
     const uint32_t ring0 = smem_u32(smem + p.ring_offset);   // same offset in every rank's shared memory
     // Rank r finalises a slice of the (tok, n_local) space (n fastest -> coalesced stores).  An output is
     // the sum of S * wk partials - K slice w of rank q lives in the ring of warp (w * wn + n_local / 32) -
@@ -431,12 +460,76 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         }
         const int n = blockIdx.x * nloc + nl;
         if (n < p.N) {
-            __half h = __float2half_rn(s);
-            if (p.bias) h = __hadd(h, p.bias[n]);
-            p.out[(size_t)(tok0 + tok) * p.N + n] = h;
+            if (fused) {
+                // this rank's fp32 partial goes into slot [half][rank] of EVERY rank's exchange buffer (own included)
+                const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
+#pragma unroll
+                for (int d = 0; d < kExchangeMaxWorld; ++d)
+                    if (d < p.world) reinterpret_cast<float*>(p.peer[d] + kExchangeDataOffset)[idx] = s;
+            } else {
+                __half h = __float2half_rn(s);
+                if (p.bias) h = __hadd(h, p.bias[n]);
+                p.out[(size_t)(tok0 + tok) * p.N + n] = h;
+            }
         }
     }
     if (S > 1) cluster.sync();                              // peers may still be reading this CTA's partials
+    if (fused) {
+        // Exchange step.  CTA i of every rank covers the same outputs (all ranks launch the same shape), so the
+        // hand-shake is per CTA: tell every rank that this rank's slice has landed, wait until every rank's
+        // slice has landed here, then add the `world` partials in rank order - the same order on every rank, so
+        // all ranks end up with bit-identical outputs.
+        __syncthreads();                                    // all pushes of this CTA are issued
+        const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+        const size_t fidx = ((size_t)half_sel * kExchangeMaxCtas + cta) * kExchangeMaxWorld;
+        if ((int)threadIdx.x < p.world) {
+            unsigned char* dst = p.self;
+#pragma unroll
+            for (int d = 0; d < kExchangeMaxWorld; ++d)
+                if (d == (int)threadIdx.x) dst = p.peer[d];
+            __threadfence_system();
+            st_release_sys_u32(reinterpret_cast<unsigned*>(dst + kExchangeFlagsOffset) + fidx + p.rank, tag);
+            const unsigned* mine = reinterpret_cast<const unsigned*>(p.self + kExchangeFlagsOffset) + fidx + threadIdx.x;
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t polls = 0;
+            // once a wait has given up the buffer stays marked and later calls do not wait at all: the job is lost
+            // either way and must not take 2 s per call to find out
+            const bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;
+            while (!dead && ld_acquire_sys_u32(mine) != tag) {
+                if ((++polls & 255u) == 0 && globaltimer_ns() - t0 > kPeerWaitBudgetNs) {
+                    atomicExch(p.error, 2);
+                    atomicExch(&hdr->error, 1 + (int)threadIdx.x);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        const float* data = reinterpret_cast<const float*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+            const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+            const int n = blockIdx.x * nloc + nl;
+            if (n >= p.N) continue;
+            const size_t idx = (size_t)(tok0 + tok) * p.N + n;
+            float v[kExchangeMaxWorld];
+#pragma unroll
+            for (int src = 0; src < kExchangeMaxWorld; ++src) v[src] = src < p.world ? __ldcg(data + (size_t)src * p.capacity + idx) : 0.f;
+            float s = v[0];
+#pragma unroll
+            for (int src = 1; src < kExchangeMaxWorld; ++src) s += v[src];
+            __half h = __float2half_rn(s);
+            if (p.bias) h = __hadd(h, p.bias[n]);
+            p.out[idx] = h;
+        }
+        // the last CTA to get here advances the epoch; the next call then uses the other half of the buffers
+        if (threadIdx.x == 0) {
+            const unsigned done = atomicAdd(&hdr->ticket, 1u);
+            if (done == gridDim.x * gridDim.y - 1) {
+                hdr->ticket = 0;
+                __threadfence();
+                *reinterpret_cast<volatile unsigned*>(&hdr->epoch) = epoch + 1;
+            }
+        }
+    }
     if (tl) tl[7] = globaltimer_ns();
 }
 
@@ -561,11 +654,14 @@ void skinny_force_config(int wn, int splits)
 int launch_skinny(const GemmArgs& a, cudaStream_t st)
 {
     if (a.tokens == 0) return W4A16_OK;
-    Config c = pick_config(a.tokens, a.N, a.K, a.g);
+    // with the fused exchange every rank must launch the same shape: choose it from the K all ranks agreed on
+    const int k_config = a.exchange ? a.exchange->k_config : a.K;
+    if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;
+    Config c = pick_config(a.tokens, a.N, k_config, a.g);
     if (c.depth < 2) return W4A16_ERR_BAD_SHAPE;         // forced configuration does not fit in shared memory
     const int kUnitK = unit_k_for(c.tg), kUnitTiles = kUnitK / kTileK;
     const int units = (a.K + kUnitK - 1) / kUnitK;
-    if (c.splits > units) c.splits = 1;
+    if (c.splits > (k_config + kUnitK - 1) / kUnitK) c.splits = 1;
     const int kWarps = c.warps;
     if (c.wn != 1 && c.wn != 2 && c.wn != 4 && c.wn != 8 && c.wn != 16 && c.wn != 32) return W4A16_ERR_BAD_ALGO;
     if (c.wn > kWarps) return W4A16_ERR_BAD_ALGO;
@@ -575,6 +671,19 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     p.x = a.x; p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out;
     p.error = device_error_word();
     if (!p.error) return W4A16_ERR_CUDA;
+    p.world = 0; p.rank = 0; p.capacity = 0; p.self = nullptr;
+    for (int d = 0; d < kExchangeMaxWorld; ++d) p.peer[d] = nullptr;
+    if (a.exchange) {
+        const ExchangeArgs& x = *a.exchange;
+        if (x.world < 1 || x.world > kExchangeMaxWorld || x.rank < 0 || x.rank >= x.world) return W4A16_ERR_BAD_SHAPE;
+        if (a.tokens > 8 * c.tg) return W4A16_ERR_TOO_LARGE;                          // one pass of at most 32 tokens
+        if ((long long)a.tokens * a.N > x.capacity) return W4A16_ERR_TOO_LARGE;
+        for (int d = 0; d < x.world; ++d) {
+            if (!x.peer[d]) return W4A16_ERR_NULL_POINTER;
+            p.peer[d] = x.peer[d];
+        }
+        p.world = x.world; p.rank = x.rank; p.capacity = x.capacity; p.self = x.peer[x.rank];
+    }
     p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
@@ -585,6 +694,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     const int n_tiles = a.N / kTileN;
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
+    if (a.exchange && (grid.z != 1 || grid.x * grid.y > (unsigned)kExchangeMaxCtas)) return W4A16_ERR_TOO_LARGE;
     // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words
     CUtensorMap wmap;
     {

@@ -39,6 +39,16 @@ C_ABI = {
     "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
     "w4a16_gemm_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
     "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
+    "w4a16_exchange_bytes": (_sz, [_ci, _sz]),
+    "w4a16_exchange_alloc": (_ci, [_ci, _sz, ctypes.POINTER(_vp)]),
+    "w4a16_exchange_free": (_ci, [_vp]),
+    "w4a16_exchange_export": (_ci, [_vp, _vp]),
+    "w4a16_exchange_open": (_ci, [_vp, ctypes.POINTER(_vp)]),
+    "w4a16_exchange_close": (_ci, [_vp]),
+    "w4a16_exchange_status": (_ci, [_vp, ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(_ci)]),
+    "w4a16_exchange_allgather": (_ci, [_vp, _vp, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz, _vp]),
+    "w4a16_gemm_allreduce": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz,
+                                   _vp, ctypes.c_uint]),
     "w4a16_gemm_static_scratch": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp]),
     "w4a16_static_scratch_error_flag": (_ci, [ctypes.POINTER(_ci)]),
     "w4a16_dequant": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
@@ -152,6 +162,39 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
                                ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo),
                                FLAG_STATIC_WEIGHTS if static_weights else 0)
     _check(st, "gemm_awq_ut")
+    return out
+
+
+def gemm_awq_allreduce(I, W, W_zeros_scales, bias, N: int, group_size: int, k_config: int, buffers, world: int,
+                       rank: int, capacity: int, out=None, static_weights: bool = False):
+    """Row-parallel linear for decode: this rank's K shard times its slice of the activations, summed over the
+    ranks inside the kernel through peer memory (see w4a16_gemm_allreduce in include/w4a16_b200.h).
+
+    I fp16 [b, s, K_shard] with b*s <= 32; `buffers` is a ctypes array of `world` device pointers (every rank's
+    exchange buffer, own included); `bias` (N elements or None) must be the same on all ranks and is added once.
+    Returns fp16 [b, s, N], identical on every rank.
+    """
+    _check_tensor(I, "I", dtype=torch.float16, dims=3)
+    _check_tensor(W, "W", dims=2)
+    _check_tensor(W_zeros_scales, "W_zeros_scales", dtype=torch.float16, dims=2)
+    b, s, K = I.shape
+    N, group_size = int(N), int(group_size)
+    _need(b * s <= 32, "gemm_awq_allreduce handles at most 32 tokens")
+    _need(W.numel() * W.element_size() * 2 == K * N, f"Tensor W must hold K*N/2 = {K * N // 2} bytes of packed int4")
+    _need(group_size > 0 and K % group_size == 0 and W_zeros_scales.numel() == (K // group_size) * N * 2,
+          "Tensor W_zeros_scales must have K/group_size * 2N elements")
+    if bias is not None:
+        _check_tensor(bias, "bias", dtype=torch.float16)
+        _need(bias.numel() == N, "Tensor bias must have N elements")
+    if out is None:
+        out = torch.empty((b, s, N), dtype=torch.float16, device=I.device)
+    lib = load_library()
+    with torch.cuda.device(I.device):
+        st = lib.w4a16_gemm_allreduce(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, out.data_ptr(), b * s, N, K,
+                                      group_size, int(k_config), buffers, int(world), int(rank), int(capacity),
+                                      _stream(I), FLAG_STATIC_WEIGHTS if static_weights else 0)
+    _check(st, "gemm_awq_allreduce")
     return out
 
 

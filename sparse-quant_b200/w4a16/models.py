@@ -80,7 +80,7 @@ class RMSNorm(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, group, device, seed: int):
+    def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, group, device, seed: int, exchange=None):
         super().__init__()
         self.cfg, self.rank, self.world = cfg, rank, world
         H, g = cfg.hidden, cfg.group_size
@@ -96,7 +96,7 @@ class DecoderLayer(nn.Module):
             return ColumnParallelWALinear(synthetic_walinear(H, n_out, g, bias, s + i, device), rank, world, ranges=ranges)
 
         self.q_proj, self.k_proj, self.v_proj = col(0, H, head_ranges), col(1, H, head_ranges), col(2, H, head_ranges)
-        self.out_proj = RowParallelWALinear(synthetic_walinear(H, H, g, bias, s + 3, device), rank, world, group, ranges=head_ranges)
+        self.out_proj = RowParallelWALinear(synthetic_walinear(H, H, g, bias, s + 3, device), rank, world, group, ranges=head_ranges, exchange=exchange)
         if cfg.kind == "opt":
             self.fc1 = col(4, cfg.ffn, ffn_ranges)
             self.ln1 = nn.LayerNorm(H, device=device, dtype=torch.float16)
@@ -104,7 +104,7 @@ class DecoderLayer(nn.Module):
         else:
             self.gate_proj, self.up_proj = col(4, cfg.ffn, ffn_ranges), col(5, cfg.ffn, ffn_ranges)
             self.ln1, self.ln2 = RMSNorm(H, cfg.rms_eps, device), RMSNorm(H, cfg.rms_eps, device)
-        self.fc2 = RowParallelWALinear(synthetic_walinear(cfg.ffn, H, g, bias, s + 6, device), rank, world, group, ranges=ffn_ranges)
+        self.fc2 = RowParallelWALinear(synthetic_walinear(cfg.ffn, H, g, bias, s + 6, device), rank, world, group, ranges=ffn_ranges, exchange=exchange)
         self.k_cache = self.v_cache = None
 
     def alloc_cache(self, batch, max_len, device):
@@ -173,9 +173,14 @@ def apply_rope(x, cos, sin):
 
 
 class Decoder(nn.Module):
-    def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, group=None, device="cuda", seed: int = 1234):
+    def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, group=None, device="cuda", seed: int = 1234,
+                 exchange=None):
+        """exchange: a tp.PeerExchange (capacity >= 32 * hidden).  With it the one-token step contains no library
+        collective: row-parallel sums are done inside the decode kernel and the ranks' best logits are gathered
+        through the same buffers, so the step can be captured in a CUDA graph at any world size."""
         super().__init__()
         self.cfg, self.rank, self.world, self.group, self.device = cfg, rank, world, group, torch.device(device)
+        self.exchange = exchange
         gen = torch.Generator(device=device).manual_seed(seed)
         H = cfg.hidden
         self.embed = (torch.randn((cfg.vocab, H), device=device, generator=gen) * 0.02).to(torch.float16)
@@ -194,7 +199,7 @@ class Decoder(nn.Module):
         v0, v1 = self.vocab_ranges[rank]
         head_full = self.embed if cfg.kind == "opt" else (torch.randn((cfg.vocab, H), device=device, generator=gen) * 0.02).to(torch.float16)
         self.lm_head = head_full[v0:v1].contiguous()
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, rank, world, group, device, seed) for i in range(cfg.layers))
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, rank, world, group, device, seed, exchange) for i in range(cfg.layers))
         self.pos = 0
 
     def mark_static(self):
@@ -245,6 +250,14 @@ class Decoder(nn.Module):
         for layer in self.layers:
             x = layer.forward_static(x, pos_t, mask, rope)
         logits = self.final_norm(x[:, -1]) @ self.lm_head.t()
+        if self.world > 1 and self.exchange is not None:
+            # each rank's best (logit, vocabulary index) of its shard; ties go to the lowest rank = lowest index
+            val, idx = logits.float().max(-1)
+            mine = torch.stack((val, (idx + self.vocab_ranges[self.rank][0]).float())).contiguous()     # [2, B] fp32
+            every = self.exchange.allgather(mine)                                                        # [world, 2, B]
+            best = every[:, 0].argmax(0, keepdim=True)                                                   # [1, B]
+            pos_t += 1
+            return every[:, 1].gather(0, best).t().long()
         if self.world > 1:
             parts = [torch.empty_like(logits) for _ in range(self.world)]
             dist.all_gather(parts, logits.contiguous(), group=self.group)
@@ -283,6 +296,9 @@ class Decoder(nn.Module):
                 nxt = self.step_static(tok, pos_t, arange)
                 tok.copy_(nxt)
             torch.cuda.synchronize(dev)
+            if self.world > 1:
+                dist.barrier(group=self.group)                 # capture takes host time: start the replays together
+                torch.cuda.synchronize(dev)
             t1b = time.perf_counter()
             for i in range(1, new_tokens):
                 graph.replay()

@@ -91,20 +91,113 @@ class ColumnParallelWALinear(nn.Module):
         return self.linear(x)
 
 
-class RowParallelWALinear(nn.Module):
-    """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1]^T (+ b on rank 0), fp16 all-reduce over `group`."""
+class PeerExchange:
+    """The exchange buffers of the decode GEMV fused with its all-reduce: one device buffer per rank, every rank's
+    buffer mapped into every process through CUDA IPC (all ranks on one node, GPUs peer-accessible).
 
-    def __init__(self, full: WALinear, rank: int, world: int, group=None, ranges=None):
+    capacity = the largest tokens * N of any call that will use it (tokens <= 32).  One object serves all
+    row-parallel linears of a model, as long as every rank issues the same calls in the same order on one stream.
+    Collective constructor: every rank of `group` must call it.  world == 1 (or no process group) gives a
+    single-rank exchange, useful for exercising the kernel path on one GPU.
+    """
+
+    def __init__(self, capacity: int, group=None, device=None):
+        import ctypes
+
+        import quant
+        self.lib = quant.load_library()
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        self.capacity = int(capacity)
+        self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        self.buffers = (ctypes.c_void_p * 8)()
+        self._opened = []
+        with torch.cuda.device(self.device):
+            own = ctypes.c_void_p()
+            quant._check(self.lib.w4a16_exchange_alloc(self.world, self.capacity, ctypes.byref(own)), "exchange_alloc")
+            self._own = own
+            self.buffers[self.rank] = own.value
+            if self.world > 1:
+                handle = (ctypes.c_ubyte * 64)()
+                quant._check(self.lib.w4a16_exchange_export(own, handle), "exchange_export")
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle), group=group)
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        continue
+                    peer = ctypes.c_void_p()
+                    raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                    quant._check(self.lib.w4a16_exchange_open(raw, ctypes.byref(peer)), "exchange_open")
+                    self._opened.append(peer)
+                    self.buffers[r] = peer.value
+                dist.barrier(group=group)          # every buffer is zeroed and mapped before anyone's first call
+
+    def allgather(self, t: torch.Tensor) -> torch.Tensor:
+        """t: contiguous CUDA tensor of a 4-byte dtype with at most `capacity` elements, same shape on every rank
+        -> [world, *t.shape], identical on every rank.  Runs on the current stream; capturable."""
+        import quant
+        assert t.is_cuda and t.is_contiguous() and t.element_size() == 4 and 0 < t.numel() <= self.capacity
+        out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        with torch.cuda.device(t.device):
+            quant._check(self.lib.w4a16_exchange_allgather(t.data_ptr(), out.data_ptr(), t.numel(), self.buffers, self.world,
+                                                           self.rank, self.capacity,
+                                                           torch.cuda.current_stream(t.device).cuda_stream), "exchange_allgather")
+        return out
+
+    def status(self):
+        """-> (calls completed on this rank, error field: 0 or 1 + rank of the peer a wait gave up on)."""
+        import ctypes
+
+        import quant
+        epoch, err = ctypes.c_uint(0), ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            quant._check(self.lib.w4a16_exchange_status(self._own, ctypes.byref(epoch), ctypes.byref(err)), "exchange_status")
+        return epoch.value, err.value
+
+    def close(self):
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self.lib.w4a16_exchange_close(p)
+            self._opened = []
+            if self._own is not None:
+                self.lib.w4a16_exchange_free(self._own)
+                self._own = None
+
+
+class RowParallelWALinear(nn.Module):
+    """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1]^T + b.
+
+    Two routes to the sum: `exchange` given and at most 32 tokens -> the decode kernel adds the ranks' fp32
+    partial sums itself through peer memory (bias added once after the sum); otherwise the local product is
+    rounded to fp16 (bias on rank 0) and summed by an fp16 all-reduce over `group`."""
+
+    def __init__(self, full: WALinear, rank: int, world: int, group=None, ranges=None, exchange=None):
         super().__init__()
         g = full.group_size
         ranges = ranges or shard_ranges(full.in_features, math.lcm(32, g), world)
         self.k0, self.k1 = ranges[rank]
+        self.k_config = max(k1 - k0 for k0, k1 in ranges)
         w, zs, b = shard_row(full.weight, full.zeros_scales, full.bias, self.k0, self.k1, g, with_bias=(rank == 0))
         self.linear = _from_buffers(w, zs, b, g)
+        self.register_buffer("full_bias", None if full.bias is None else full.bias.detach().clone())
         self.group = group
         self.world = world
+        self.rank = rank
+        self.exchange = exchange
 
     def forward(self, x_local):
+        tokens = x_local.numel() // x_local.shape[-1]
+        if self.exchange is not None and tokens <= 32 and tokens * self.linear.out_features <= self.exchange.capacity:
+            from quant import gemm_awq_allreduce
+            lin = self.linear
+            x3 = x_local.reshape(1, tokens, x_local.shape[-1])
+            if not x3.is_contiguous():
+                x3 = x3.contiguous()
+            y = gemm_awq_allreduce(x3, lin.weight, lin.zeros_scales, self.full_bias, lin.out_features, lin.group_size,
+                                   self.k_config, self.exchange.buffers, self.exchange.world, self.exchange.rank,
+                                   self.exchange.capacity, static_weights=lin.static_weights)
+            return y.reshape(*x_local.shape[:-1], lin.out_features)
         y = self.linear(x_local)
         if self.world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
