@@ -135,11 +135,13 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
 // ---------------------------------------------------------------------------------------------
 // Exchange buffer of one rank for the GEMV fused with its all-reduce (row-parallel linears): every rank owns one
 // such buffer and maps all its peers' buffers.  Layout:
-//   [ExchangeHeader, 256 B][flags: 2 halves x kExchangeMaxCtas x kExchangeMaxWorld u32][data: 2 halves x world x capacity fp32]
-constexpr int    kExchangeMaxWorld  = 8;
-constexpr int    kExchangeMaxCtas   = 256;
-constexpr size_t kExchangeFlagsOffset = 256;
-constexpr size_t kExchangeDataOffset  = kExchangeFlagsOffset + 2 * (size_t)kExchangeMaxCtas * kExchangeMaxWorld * 4;
+//   [ExchangeHeader, 256 B][data: 2 halves x world x capacity slots of 8 bytes]
+// A slot is (32-bit payload, 32-bit tag) written with ONE 8-byte store, which arrives atomically: the receiver
+// polls the slot itself until the tag is the current call's - no separate flag, no fence, one NVLink crossing.
+// Tags are epoch + 1, unique per call, so stale slots of earlier calls never match; the two halves alternate so
+// that a rank already in the next call cannot overwrite slots a slower rank is still reading.
+constexpr int    kExchangeMaxWorld   = 8;
+constexpr size_t kExchangeDataOffset = 256;
 struct ExchangeHeader {
     unsigned epoch;     // calls completed on this rank; selects the buffer half (epoch & 1) and the flag value (epoch + 1)
     unsigned ticket;    // CTAs of the running call that are done; the last one advances `epoch`

@@ -2,8 +2,9 @@
 //
 // A row-parallel linear (out_proj / fc2 / o_proj / down_proj under tensor parallelism) multiplies its K shard and
 // then needs the sum over ranks.  For decode-sized inputs the sum is done inside the GEMV kernel: each CTA pushes
-// its fp32 partial outputs over NVLink into every rank's exchange buffer, raises a flag there, waits (bounded) for
-// the matching CTAs of the other ranks, and adds the `world` partials in rank order.  No NCCL call, nothing that a
+// its fp32 partial outputs over NVLink into every rank's exchange buffer as (value, tag) pairs in single 8-byte
+// stores, polls (bounded) its own buffer until every rank's pair carries the call's tag, and adds the `world`
+// partials in rank order.  No NCCL call, nothing that a
 // stream capture cannot record; partials stay fp32 until the single final rounding.
 //
 // The buffers are ordinary device allocations shared through CUDA IPC: w4a16_exchange_alloc on every rank, the
@@ -33,10 +34,10 @@ struct GatherParams {
     long long capacity;
 };
 
-// All-gather of a few 32-bit words per rank through the exchange buffers (one CTA): push this rank's words into
-// slot [half][rank] of every rank's buffer, raise the flag of CTA 0 there, wait (bounded) for every rank's flag
-// here, copy the `world` slots out in rank order, advance the epoch.  Same protocol as the fused GEMV epilogue,
-// so the two can be mixed on one set of buffers.
+// All-gather of a few 32-bit words per rank through the exchange buffers (one CTA): write (word, tag) into slot
+// [half][rank][i] of every rank's buffer, poll this rank's `world` slots of word i until all carry this call's tag,
+// copy them out in rank order, advance the epoch.  Same protocol as the fused GEMV epilogue, so the two can be
+// mixed on one set of buffers.
 __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherParams p)
 {
     ExchangeHeader* hdr = reinterpret_cast<ExchangeHeader*>(p.self);
@@ -47,36 +48,30 @@ __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherPar
         const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + i;
 #pragma unroll
         for (int d = 0; d < kExchangeMaxWorld; ++d)
-            if (d < p.world) reinterpret_cast<unsigned*>(p.peer[d] + kExchangeDataOffset)[idx] = v;
+            if (d < p.world)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx), "r"(v), "r"(tag) : "memory");
     }
-    __syncthreads();
-    const size_t fidx = (size_t)half_sel * kExchangeMaxCtas * kExchangeMaxWorld;       // flags of CTA 0
-    if ((int)threadIdx.x < p.world) {
-        unsigned char* dst = p.self;
-#pragma unroll
-        for (int d = 0; d < kExchangeMaxWorld; ++d)
-            if (d == (int)threadIdx.x) dst = p.peer[d];
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(dst + kExchangeFlagsOffset) + fidx + p.rank), "r"(tag) : "memory");
-        const unsigned* mine = reinterpret_cast<const unsigned*>(p.self + kExchangeFlagsOffset) + fidx + threadIdx.x;
-        const unsigned long long t0 = timer_ns();
-        unsigned polls = 0, seen = 0;
-        const bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;     // an earlier wait gave up: do not wait again
-        while (!dead) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if (seen == tag) break;
-            if ((++polls & 255u) == 0 && timer_ns() - t0 > 2000000000ull) {
-                atomicExch(p.error, 2);
-                atomicExch(&hdr->error, 1 + (int)threadIdx.x);
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    const unsigned* data = reinterpret_cast<const unsigned*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+    const uint2* data = reinterpret_cast<const uint2*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+    bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;      // an earlier wait gave up: do not wait again
     for (int i = threadIdx.x; i < p.words * p.world; i += blockDim.x) {
         const int src = i / p.words, w = i - src * p.words;
-        p.out[i] = __ldcg(data + (size_t)src * p.capacity + w);
+        const uint2* slot = data + (size_t)src * p.capacity + w;
+        uint2 v;
+        unsigned long long t0 = 0;
+        for (unsigned polls = 0;; ++polls) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(slot) : "memory");
+            if (v.y == tag || dead) break;
+            if ((polls & 255u) == 255u) {
+                const unsigned long long now = timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > 2000000000ull) {
+                    atomicExch(p.error, 2);
+                    atomicExch(&hdr->error, 1 + src);
+                    dead = true;
+                }
+            }
+        }
+        p.out[i] = v.x;
     }
     __syncthreads();
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned*>(&hdr->epoch) = epoch + 1;
@@ -87,7 +82,7 @@ __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherPar
 extern "C" size_t w4a16_exchange_bytes(int world, size_t capacity_elems)
 {
     if (world < 1 || world > kExchangeMaxWorld) return 0;
-    return kExchangeDataOffset + 2 * (size_t)world * capacity_elems * sizeof(float);
+    return kExchangeDataOffset + 2 * (size_t)world * capacity_elems * 8;   // (payload, tag) slots
 }
 
 extern "C" int w4a16_exchange_alloc(int world, size_t capacity_elems, void** buffer)

@@ -193,14 +193,14 @@ __device__ __forceinline__ void compute_unit(const Slot<G, kUnitK>* slot, float 
     }
 }
 
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v)
+__device__ __forceinline__ void st_slot(uint2* p, uint2 v)          // one 8-byte store: payload and tag land together
 {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p)
+__device__ __forceinline__ uint2 ld_slot(const uint2* p)
 {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 constexpr uint64_t kPeerWaitBudgetNs = 2000ull * 1000 * 1000;     // a peer that does not show up within 2 s is given up on
@@ -262,36 +262,24 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(smem)[threadIdx.x] = 0u;
     if (lane == 0) {
         for (int i = 0; i < kDepth; ++i) mbar_init(bars + 8 * i, 1);
+        if (warp == 0) mbar_init(smem_u32(smem) + 24, 1);       // the activations' barrier
         mbar_fence_init();
     }
 
-    // Activations x[tok0 .. tok0+rows) x [cu0*128, cu1*128) are staged in shared memory (zero beyond K);
-    // token rows past `rows` all read the 16 zero bytes at the start of shared memory.
+    // Activations x[tok0 .. tok0+rows) x [this CTA's K range] are staged in shared memory by bulk copies, one per
+    // token row, all completing on one mbarrier; the part of the range beyond K (last units only) is zero-filled
+    // by hand.  Token rows past `rows` all read the 16 zero bytes at the start of shared memory.
     const int kc0 = cu0 * kUnitK;
-    const int vec_per_row = cta_units * (kUnitK / 8);
-    const int total = (kDebug && (p.debug_mode & 2)) ? 0 : rows * vec_per_row;
-    const unsigned vpr_inv = vec_per_row > 1 ? 0xffffffffu / (unsigned)vec_per_row + 1u : 0u;   // i / vpr == umulhi(i, inv) for i < 2^16 * vpr
-    auto div_vpr = [&](int i) { return vec_per_row > 1 ? (int)__umulhi((unsigned)i, vpr_inv) : i; };
-    constexpr int kBatch = 8;                               // 16-byte loads in flight per thread
-    uint4 xval[kBatch];
-    int xdst[kBatch];
-    auto load_x_batch = [&](int base) {
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-            const int i = base + j * kThreads;
-            xval[j] = make_uint4(0, 0, 0, 0);
-            xdst[j] = -1;
-            if (i < total) {
-                const int row = div_vpr(i), v = i - row * vec_per_row;
-                xdst[j] = row * p.xs_stride + v * 8;
-                if (kc0 + v * 8 < p.K) xval[j] = *reinterpret_cast<const uint4*>(p.x + (size_t)(tok0 + row) * p.K + kc0 + v * 8);
-            }
+    const int row_halfs = cta_units * kUnitK;                                  // staged k per row
+    const int copy_halfs = max(0, min(row_halfs, p.K - kc0));                 // of which exist in x
+    const uint32_t xbar = smem_u32(smem) + 24;
+    const bool stage_x = !(kDebug && (p.debug_mode & 2)) && copy_halfs > 0;
+    auto issue_x = [&]() {
+        if (threadIdx.x == 0 && stage_x) {
+            mbar_arrive_expect_tx(xbar, (uint32_t)rows * (uint32_t)copy_halfs * 2u);
+            for (int row = 0; row < rows; ++row)
+                bulk_load(smem_u32(xs) + (uint32_t)(row * p.xs_stride) * 2u, p.x + (size_t)(tok0 + row) * p.K + kc0, (uint32_t)copy_halfs * 2u, xbar);
         }
-    };
-    auto store_x_batch = [&]() {
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j)
-            if (xdst[j] >= 0) *reinterpret_cast<uint4*>(xs + xdst[j]) = xval[j];
     };
     const uint32_t ring_addr = smem_u32(ring);
     const int groups = p.K / G;
@@ -312,20 +300,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         issue_first_units();
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        load_x_batch(threadIdx.x);
+        issue_x();
     } else {
-        // The activation loads are issued BEFORE the weight copies (they are on the critical path and must
-        // not queue behind megabytes of weight traffic) and stored after the copies are in flight.
-        load_x_batch(threadIdx.x);
+        // The activation copies are issued BEFORE the weight copies: they are on the critical path and must
+        // not queue behind megabytes of weight traffic.
+        issue_x();
         issue_first_units();
     }
-    store_x_batch();
-    for (int base = threadIdx.x + kBatch * kThreads; base < total; base += kThreads * kBatch) {   // long rows: further batches
-        load_x_batch(base);
-        store_x_batch();
+    if (copy_halfs < row_halfs) {                               // K edge: zeros behind the copied part of every row
+        const int tail_vec = (row_halfs - copy_halfs) / 8;
+        for (int i = threadIdx.x; i < rows * tail_vec; i += kThreads) {
+            const int row = i / tail_vec, v = i - row * tail_vec;
+            *reinterpret_cast<uint4*>(xs + row * p.xs_stride + copy_halfs + v * 8) = make_uint4(0, 0, 0, 0);
+        }
     }
+    __syncthreads();                                            // barrier initialised, zero tail written
+    if (stage_x) mbar_wait(xbar, 0, abort_flag, kWaitBudgetNs);
     if (tl) tl[1] = globaltimer_ns();
-    __syncthreads();
 
     // sum_k x[t, k] per quantisation group of this CTA's K range, once per CTA: an MMA with an all-ones A
     // fragment over the staged activations (every row of the result holds the sums), groups dealt round-robin
@@ -465,7 +456,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                 const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
 #pragma unroll
                 for (int d = 0; d < kExchangeMaxWorld; ++d)
-                    if (d < p.world) reinterpret_cast<float*>(p.peer[d] + kExchangeDataOffset)[idx] = s;
+                    if (d < p.world) st_slot(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx, make_uint2(__float_as_uint(s), tag));
             } else {
                 __half h = __float2half_rn(s);
                 if (p.bias) h = __hadd(h, p.bias[n]);
@@ -475,51 +466,53 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     }
     if (S > 1) cluster.sync();                              // peers may still be reading this CTA's partials
     if (fused) {
-        // Exchange step.  CTA i of every rank covers the same outputs (all ranks launch the same shape), so the
-        // hand-shake is per CTA: tell every rank that this rank's slice has landed, wait until every rank's
-        // slice has landed here, then add the `world` partials in rank order - the same order on every rank, so
-        // all ranks end up with bit-identical outputs.
-        __syncthreads();                                    // all pushes of this CTA are issued
-        const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-        const size_t fidx = ((size_t)half_sel * kExchangeMaxCtas + cta) * kExchangeMaxWorld;
-        if ((int)threadIdx.x < p.world) {
-            unsigned char* dst = p.self;
-#pragma unroll
-            for (int d = 0; d < kExchangeMaxWorld; ++d)
-                if (d == (int)threadIdx.x) dst = p.peer[d];
-            __threadfence_system();
-            st_release_sys_u32(reinterpret_cast<unsigned*>(dst + kExchangeFlagsOffset) + fidx + p.rank, tag);
-            const unsigned* mine = reinterpret_cast<const unsigned*>(p.self + kExchangeFlagsOffset) + fidx + threadIdx.x;
-            const uint64_t t0 = globaltimer_ns();
-            uint32_t polls = 0;
-            // once a wait has given up the buffer stays marked and later calls do not wait at all: the job is lost
-            // either way and must not take 2 s per call to find out
-            const bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;
-            while (!dead && ld_acquire_sys_u32(mine) != tag) {
-                if ((++polls & 255u) == 0 && globaltimer_ns() - t0 > kPeerWaitBudgetNs) {
-                    atomicExch(p.error, 2);
-                    atomicExch(&hdr->error, 1 + (int)threadIdx.x);
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-        const float* data = reinterpret_cast<const float*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+        // Exchange step.  CTA i of every rank covers the same outputs (all ranks launch the same shape) and thread j
+        // the same elements, so each thread polls the slots of exactly the elements it pushed: all `world` slots of
+        // an element are re-read until every tag is this call's, then the partials are added in rank order - the
+        // same order on every rank, so all ranks end up with bit-identical outputs.
+        const uint2* data = reinterpret_cast<const uint2*>(p.self + kExchangeDataOffset) + (size_t)half_sel * p.world * p.capacity;
+        // once a wait has given up the buffer stays marked and later calls do not wait at all: the job is lost
+        // either way and must not take seconds per call to find out
+        bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;
         for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
             const int tok = e >> nloc_shift, nl = e & (nloc - 1);
             const int n = blockIdx.x * nloc + nl;
             if (n >= p.N) continue;
             const size_t idx = (size_t)(tok0 + tok) * p.N + n;
-            float v[kExchangeMaxWorld];
+            uint2 v[kExchangeMaxWorld];
+            uint64_t t0 = 0;
+            for (uint32_t polls = 0;; ++polls) {
+                bool all = true;
 #pragma unroll
-            for (int src = 0; src < kExchangeMaxWorld; ++src) v[src] = src < p.world ? __ldcg(data + (size_t)src * p.capacity + idx) : 0.f;
-            float s = v[0];
+                for (int src = 0; src < kExchangeMaxWorld; ++src)
+                    if (src < p.world) {
+                        v[src] = ld_slot(data + (size_t)src * p.capacity + idx);
+                        all = all && v[src].y == tag;
+                    }
+                if (all || dead) break;
+                if ((polls & 255u) == 255u) {
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > kPeerWaitBudgetNs) {
+                        int late = 0;
 #pragma unroll
-            for (int src = 1; src < kExchangeMaxWorld; ++src) s += v[src];
+                        for (int src = 0; src < kExchangeMaxWorld; ++src)
+                            if (src < p.world && v[src].y != tag) late = src;
+                        atomicExch(p.error, 2);
+                        atomicExch(&hdr->error, 1 + late);
+                        dead = true;
+                    }
+                }
+            }
+            float s = __uint_as_float(v[0].x);
+#pragma unroll
+            for (int src = 1; src < kExchangeMaxWorld; ++src)
+                if (src < p.world) s += __uint_as_float(v[src].x);
             __half h = __float2half_rn(s);
             if (p.bias) h = __hadd(h, p.bias[n]);
             p.out[idx] = h;
         }
+        __syncthreads();
         // the last CTA to get here advances the epoch; the next call then uses the other half of the buffers
         if (threadIdx.x == 0) {
             const unsigned done = atomicAdd(&hdr->ticket, 1u);
@@ -694,7 +687,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     const int n_tiles = a.N / kTileN;
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
-    if (a.exchange && (grid.z != 1 || grid.x * grid.y > (unsigned)kExchangeMaxCtas)) return W4A16_ERR_TOO_LARGE;
+    if (a.exchange && grid.z != 1) return W4A16_ERR_TOO_LARGE;
     // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words
     CUtensorMap wmap;
     {
