@@ -81,8 +81,11 @@ int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales
  * stream).  The decode kernel is then launched with programmatic stream serialization: it
  * starts fetching weights while the previous kernel of the stream drains, and waits for that
  * kernel to complete before it reads x or writes out.  No counterpart in the reference.
+ * W4A16_FLAG_RELU clamps the outputs at zero after the bias add: the ReLU that follows fc1 in the reference's OPT
+ * layer (modeling_opt_ours.py:606, activation_fn) without a launch of its own.
  */
 #define W4A16_FLAG_STATIC_WEIGHTS 1u
+#define W4A16_FLAG_RELU 2u
 int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
                   void* out, int tokens, int N, int K, int group_size,
                   void* workspace, size_t workspace_bytes, void* stream, int algo, unsigned flags);
@@ -173,6 +176,43 @@ int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_s
                          void* out, int tokens, int N, int K, int group_size, int k_config,
                          void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
                          unsigned flags);
+
+/*
+ * Decode attention over a static key/value cache: one new token per sequence, one launch.  Replaces, for the
+ * decode step, the reference's torch ops around its quantised projections: torch.cat of the new key/value onto the
+ * cache (modeling_opt_ours.py:249-250), bmm(q, K^T) (:306), mask + softmax, bmm(P, V) (:456) and the
+ * transpose/reshape before out_proj.
+ *   qkv      fp16 [batch, qkv_stride], row b = [q (heads*head_dim) | k (heads*head_dim) | v (heads*head_dim)]: the output
+ *            of the q/k/v projections fused into one GEMV (unscaled q)
+ *   k_cache, v_cache  fp16 [batch, heads, max_len, head_dim]; row *pos is written, rows 0..*pos are read
+ *   out      fp16 [batch, heads*head_dim]
+ *   pos      device pointer to one int64: index of the new token (0 <= *pos < max_len, else the device error word is
+ *            set to 3 and nothing is written)
+ *   rope_cos, rope_sin  fp16 [>= *pos+1, head_dim] rotary tables ("rotate half" convention) or both NULL
+ *   scale    multiplies q.k (head_dim^-0.5 in both OPT and LLaMA)
+ * head_dim 64 or 128.  Scores, softmax and the weighted sum are fp32; outputs are rounded to fp16 once.
+ */
+int w4a16_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, const void* pos,
+                           const void* rope_cos, const void* rope_sin, int batch, int heads, int head_dim,
+                           int max_len, int qkv_stride, float scale, void* stream);
+
+/*
+ * Residual add fused with the normalisation that follows it, for decode-sized inputs.  Replaces the reference's
+ * `hidden = residual + hidden` + nn.LayerNorm (modeling_opt_ours.py:590,603-604,614,561-562) or + LlamaRMSNorm
+ * (modeling_llama_ours.py:113-118), which run as separate torch kernels.
+ *   s = fp16(x + delta) -> x_out (delta NULL: s = x, x_out unused);  h_out = norm(s)
+ *   rms == 0: LayerNorm with fp16 `weight` and `bias` (bias may be NULL), statistics and affine in fp32
+ *   rms != 0: weight * fp16(s * rsqrt(mean(s^2) + eps)), `bias` ignored
+ * x, delta, x_out, h_out fp16 [rows, cols] contiguous, cols % 8 == 0, cols <= 8192 (W4A16_ERR_TOO_LARGE beyond).
+ * x_out may alias x or delta.
+ */
+int w4a16_add_norm(const void* x, const void* delta, void* x_out, void* h_out, const void* weight, const void* bias,
+                   int rows, int cols, float eps, int rms, void* stream);
+
+/* out[r, c] = fp16(silu(gate_up[r, c])) * gate_up[r, n + c]: the SwiGLU product of the reference's LlamaMLP
+ * (act_fn(gate_proj(x)) * up_proj(x), modeling_llama_ours.py:272) on the output [rows, 2n] of the gate/up projections
+ * fused into one GEMV; fp16, n % 8 == 0. */
+int w4a16_silu_mul(const void* gate_up, void* out, int rows, int n, void* stream);
 
 /*
  * No counterpart in the reference.  The tcgen05 GEMM with K split in two, for callers that cannot

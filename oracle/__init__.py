@@ -226,3 +226,32 @@ def quant_pack(weight_fp16, group_size: int = 128):
     qw8, zeros, scales, w_fp16 = generate_quant(weight_fp16, 4, group_size)
     qweight, zs = pack(qw8, zeros, scales, K, N, group_size)
     return qweight, zs, w_fp16
+
+
+def decode_attention(q, k_new, v_new, k_cache, v_cache, pos: int, scale: float, cos=None, sin=None):
+    """Float64 restatement of one decode step of dense attention as the reference's OPT layer does it with torch
+    ops (test/nvidia/module/opt/modeling_opt_ours.py: new key/value appended to the cache :249-250, q.K^T :306,
+    softmax over the positions seen so far, P.V :456), plus the "rotate half" rotary embedding of the LLaMA-shaped
+    stack.  "Parity unpinned": the reference holds no golden vectors for attention; this is the mathematical
+    definition, compared with a stated floating-point tolerance.
+
+    q, k_new, v_new [B, H, D]; caches [B, H, L, D] (rows < pos are the past); cos/sin [D] of position `pos`.
+    Returns (out [B, H, D] float64, k_row fp16 [B, H, D] as stored in the cache, v_row fp16)."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k_new, dtype=np.float64)
+    v = np.asarray(v_new, dtype=np.float64)
+    if cos is not None:
+        d = q.shape[-1] // 2
+        c, s = np.asarray(cos, dtype=np.float64), np.asarray(sin, dtype=np.float64)
+
+        def rot(x):
+            return x * c + np.concatenate((-x[..., d:], x[..., :d]), axis=-1) * s
+        q, k = rot(q), rot(k)
+    k_row, v_row = k.astype(np.float16), v.astype(np.float16)
+    keys = np.concatenate((np.asarray(k_cache, dtype=np.float64)[:, :, :pos], k_row.astype(np.float64)[:, :, None]), axis=2)
+    vals = np.concatenate((np.asarray(v_cache, dtype=np.float64)[:, :, :pos], v_row.astype(np.float64)[:, :, None]), axis=2)
+    scores = np.einsum("bhd,bhtd->bht", q, keys) * scale
+    scores -= scores.max(axis=-1, keepdims=True)
+    p = np.exp(scores)
+    p /= p.sum(axis=-1, keepdims=True)
+    return np.einsum("bht,bhtd->bhd", p, vals), k_row, v_row

@@ -146,7 +146,7 @@ extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zer
     int s = validate(x, qweight, zeros_scales, out, tokens, N, K, group_size);
     if (s != W4A16_OK) return s;
     if (algo != W4A16_ALGO_AUTO && algo != W4A16_ALGO_SKINNY && algo != W4A16_ALGO_TC) return W4A16_ERR_BAD_ALGO;
-    if (flags & ~(unsigned)W4A16_FLAG_STATIC_WEIGHTS) return W4A16_ERR_BAD_ALGO;
+    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU)) return W4A16_ERR_BAD_ALGO;
     if (tokens == 0) return W4A16_OK;
     s = check_device();
     if (s != W4A16_OK) return s;
@@ -156,6 +156,7 @@ extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zer
     a.bias = (const __half*)bias; a.out = (__half*)out;
     a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
     a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
+    a.relu = (flags & W4A16_FLAG_RELU) != 0;
 
     if (algo == W4A16_ALGO_AUTO) algo = (tokens <= 32 || !tc_supported(tokens, N, K, group_size)) ? W4A16_ALGO_SKINNY : W4A16_ALGO_TC;
     if (algo == W4A16_ALGO_TC) {

@@ -162,6 +162,7 @@ struct GemmArgs {
     __half*         out;
     int tokens, N, K, g;
     bool static_weights;   // W4A16_FLAG_STATIC_WEIGHTS
+    bool relu = false;     // W4A16_FLAG_RELU: out = max(out, 0) after the bias add
     const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
 };
 

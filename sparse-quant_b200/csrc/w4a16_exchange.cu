@@ -41,6 +41,7 @@ struct GatherParams {
 __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherParams p)
 {
     ExchangeHeader* hdr = reinterpret_cast<ExchangeHeader*>(p.self);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&hdr->epoch);
     const unsigned half_sel = epoch & 1u, tag = epoch + 1u;
     for (int i = threadIdx.x; i < p.words; i += blockDim.x) {
@@ -160,7 +161,7 @@ extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const vo
     if (((uintptr_t)x & 15) || ((uintptr_t)qweight & 15) || ((uintptr_t)zeros_scales & 15) || ((uintptr_t)out & 15))
         return W4A16_ERR_MISALIGNED;
     if (world < 1 || world > kExchangeMaxWorld || rank < 0 || rank >= world) return W4A16_ERR_BAD_SHAPE;
-    if (flags & ~(unsigned)W4A16_FLAG_STATIC_WEIGHTS) return W4A16_ERR_BAD_ALGO;
+    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU)) return W4A16_ERR_BAD_ALGO;
     int dev = 0, major = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
@@ -175,6 +176,7 @@ extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const vo
     a.bias = (const __half*)bias; a.out = (__half*)out;
     a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
     a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
+    a.relu = (flags & W4A16_FLAG_RELU) != 0;
     a.exchange = &ex;
     return launch_skinny(a, (cudaStream_t)stream);
 }

@@ -80,6 +80,7 @@ struct SkinnyParams {
     int ring_offset; // byte offset of the per-warp rings in shared memory
     int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
+    int relu;        // clamp the outputs at zero after the bias add
     int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
     // fused all-reduce over peer memory (world == 0: plain store of this GPU's result)
     unsigned char* peer[kExchangeMaxWorld];
@@ -460,6 +461,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             } else {
                 __half h = __float2half_rn(s);
                 if (p.bias) h = __hadd(h, p.bias[n]);
+                if (p.relu) h = __hmax(h, __half());
                 p.out[(size_t)(tok0 + tok) * p.N + n] = h;
             }
         }
@@ -510,6 +512,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                 if (src < p.world) s += __uint_as_float(v[src].x);
             __half h = __float2half_rn(s);
             if (p.bias) h = __hadd(h, p.bias[n]);
+            if (p.relu) h = __hmax(h, __half());
             p.out[idx] = h;
         }
         __syncthreads();
@@ -555,10 +558,11 @@ int stage_bytes(int rows, int K, int splits, int kUnitK, int tg, int g)
     return kHeaderBytes + xs_bytes(rows, K, splits, kUnitK) + xsum_bytes(tg, K, splits, kUnitK, g);
 }
 
-Config pick_config(int tokens, int N, int K, int g)
+Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
 {
     Config c;
     c.tg = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
+    if (c.tg > max_tg) c.tg = max_tg;
     const int kUnitK = unit_k_for(c.tg);
     const int n_tiles = N / kTileN, units = (K + kUnitK - 1) / kUnitK;
     const int rows = tokens < 8 * c.tg ? tokens : 8 * c.tg;
@@ -651,6 +655,10 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
     if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;
     Config c = pick_config(a.tokens, a.N, k_config, a.g);
+    // 17..32 tokens with a K so long that the staged activations need clusters of 8 CTAs: such clusters do not
+    // always fit the machine in one wave; two passes of 16 tokens (gridDim.z, the second one reading the weights
+    // from L2) are faster.  Not with the fused exchange, which needs all tokens in one pass.
+    if (c.tg == 4 && c.splits >= 8 && !a.exchange && !g_force_splits) c = pick_config(a.tokens, a.N, k_config, a.g, 2);
     if (c.depth < 2) return W4A16_ERR_BAD_SHAPE;         // forced configuration does not fit in shared memory
     const int kUnitK = unit_k_for(c.tg), kUnitTiles = kUnitK / kTileK;
     const int units = (a.K + kUnitK - 1) / kUnitK;
@@ -677,7 +685,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
         }
         p.world = x.world; p.rank = x.rank; p.capacity = x.capacity; p.self = x.peer[x.rank];
     }
-    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0;
+    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0; p.relu = a.relu ? 1 : 0;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
     const int tok = 8 * c.tg;

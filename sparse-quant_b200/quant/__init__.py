@@ -49,6 +49,9 @@ C_ABI = {
     "w4a16_exchange_allgather": (_ci, [_vp, _vp, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz, _vp]),
     "w4a16_gemm_allreduce": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz,
                                    _vp, ctypes.c_uint]),
+    "w4a16_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.c_float, _vp]),
+    "w4a16_add_norm": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float, _ci, _vp]),
+    "w4a16_silu_mul": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_gemm_static_scratch": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp]),
     "w4a16_static_scratch_error_flag": (_ci, [ctypes.POINTER(_ci)]),
     "w4a16_dequant": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
@@ -121,16 +124,18 @@ def launch_count() -> int:
 
 
 FLAG_STATIC_WEIGHTS = 1
+FLAG_RELU = 2
 
 
 def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None,
-                  static_weights: bool = False):
+                  static_weights: bool = False, relu: bool = False):
     """gemm_awq_ut with the fp16 bias add of WALinear.forward fused into the kernel epilogue.
 
     I fp16 [b, s, K] (CUDA, contiguous); W int32 [K, N/8] tile-ordered; W_zeros_scales fp16
     [K/g, 2N]; bias fp16 with N elements or None.  Returns fp16 [b, s, N].
     static_weights=True passes W4A16_FLAG_STATIC_WEIGHTS (see include/w4a16_b200.h): only for weights
     that were written before anything still in flight on the current stream was enqueued.
+    relu=True passes W4A16_FLAG_RELU: max(., 0) applied after the bias add.
     """
     _check_tensor(I, "I", dtype=torch.float16, dims=3)
     _check_tensor(W, "W", dims=2)
@@ -160,7 +165,7 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
                                bias.data_ptr() if bias is not None else None, out.data_ptr(),
                                tokens, N, K, group_size,
                                ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo),
-                               FLAG_STATIC_WEIGHTS if static_weights else 0)
+                               (FLAG_STATIC_WEIGHTS if static_weights else 0) | (FLAG_RELU if relu else 0))
     _check(st, "gemm_awq_ut")
     return out
 
@@ -195,6 +200,73 @@ def gemm_awq_allreduce(I, W, W_zeros_scales, bias, N: int, group_size: int, k_co
                                       group_size, int(k_config), buffers, int(world), int(rank), int(capacity),
                                       _stream(I), FLAG_STATIC_WEIGHTS if static_weights else 0)
     _check(st, "gemm_awq_allreduce")
+    return out
+
+
+def add_norm(x, delta, weight, bias, eps: float, rms: bool):
+    """(x + delta, norm(x + delta)) in one launch (see w4a16_add_norm in include/w4a16_b200.h); delta None: (x, norm(x)).
+    x, delta fp16 [..., cols] contiguous; LayerNorm (rms=False, fp16 weight/bias) or RMSNorm (rms=True)."""
+    _check_tensor(x, "x", dtype=torch.float16)
+    _check_tensor(weight, "weight", dtype=torch.float16)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    _need(weight.numel() == cols, "weight must have one element per column")
+    if delta is not None:
+        _check_tensor(delta, "delta", dtype=torch.float16)
+        _need(delta.shape == x.shape, "delta must have the shape of x")
+    if bias is not None:
+        _check_tensor(bias, "bias", dtype=torch.float16)
+    s = torch.empty_like(x) if delta is not None else x
+    h = torch.empty_like(x)
+    lib = load_library()
+    with torch.cuda.device(x.device):
+        st = lib.w4a16_add_norm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                s.data_ptr() if delta is not None else None, h.data_ptr(), weight.data_ptr(),
+                                bias.data_ptr() if (bias is not None and not rms) else None, rows, cols, float(eps), int(bool(rms)),
+                                _stream(x))
+    _check(st, "add_norm")
+    return s, h
+
+
+def silu_mul(gate_up):
+    """fp16 [..., 2n] (gate | up) -> silu(gate) * up, fp16 [..., n] (see w4a16_silu_mul in include/w4a16_b200.h)."""
+    _check_tensor(gate_up, "gate_up", dtype=torch.float16)
+    n = gate_up.shape[-1] // 2
+    rows = gate_up.numel() // (2 * n)
+    out = torch.empty(tuple(gate_up.shape[:-1]) + (n,), dtype=torch.float16, device=gate_up.device)
+    lib = load_library()
+    with torch.cuda.device(gate_up.device):
+        _check(lib.w4a16_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, n, _stream(gate_up)), "silu_mul")
+    return out
+
+
+def decode_attention(qkv, k_cache, v_cache, pos, heads: int, rope=None, scale=None, out=None):
+    """One decode step of attention over a static cache (see w4a16_decode_attention in include/w4a16_b200.h).
+
+    qkv fp16 [B, >= 3*heads*D] (q | k | v of the new token), k_cache / v_cache fp16 [B, heads, max_len, D]
+    (contiguous; updated in place at row `pos`), pos int64 CUDA tensor with one element, rope = (cos, sin) fp16
+    [positions, D] tables or None.  Returns fp16 [B, heads*D]."""
+    _check_tensor(qkv, "qkv", dtype=torch.float16, dims=2)
+    _check_tensor(k_cache, "k_cache", dtype=torch.float16, dims=4)
+    _check_tensor(v_cache, "v_cache", dtype=torch.float16, dims=4)
+    B, H, max_len, D = k_cache.shape
+    _need(H == int(heads) and tuple(v_cache.shape) == tuple(k_cache.shape), "cache shape must be [B, heads, max_len, D]")
+    _need(qkv.shape[0] == B and qkv.shape[1] >= 3 * H * D, "qkv must be [B, >= 3*heads*D]")
+    _need(pos.is_cuda and pos.dtype == torch.int64 and pos.numel() == 1, "pos must be one int64 on the device")
+    cos = sin = None
+    if rope is not None:
+        cos, sin = rope
+        _check_tensor(cos, "rope cos", dtype=torch.float16, dims=2)
+        _check_tensor(sin, "rope sin", dtype=torch.float16, dims=2)
+        _need(cos.shape[1] == D and sin.shape == cos.shape and cos.shape[0] >= max_len, "rope tables must be [>= max_len, D]")
+    if out is None:
+        out = torch.empty((B, H * D), dtype=torch.float16, device=qkv.device)
+    lib = load_library()
+    with torch.cuda.device(qkv.device):
+        st = lib.w4a16_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), pos.data_ptr(),
+                                        cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+                                        B, H, D, max_len, qkv.stride(0), float(D ** -0.5 if scale is None else scale), _stream(qkv))
+    _check(st, "decode_attention")
     return out
 
 

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .qlinear import WALinear
-from .tp import ColumnParallelWALinear, RowParallelWALinear, shard_ranges
+from .tp import ColumnParallelWALinear, RowParallelWALinear, fuse_columns, shard_ranges
 
 
 @dataclass
@@ -95,14 +95,16 @@ class DecoderLayer(nn.Module):
         def col(i, n_out, ranges):
             return ColumnParallelWALinear(synthetic_walinear(H, n_out, g, bias, s + i, device), rank, world, ranges=ranges)
 
-        self.q_proj, self.k_proj, self.v_proj = col(0, H, head_ranges), col(1, H, head_ranges), col(2, H, head_ranges)
+        # q/k/v (and gate/up below) are sharded one by one, then this rank's shards are fused in the packed domain
+        # into one linear: one GEMV launch instead of three, and the layout the decode attention kernel reads
+        self.qkv_proj = fuse_columns([col(0, H, head_ranges), col(1, H, head_ranges), col(2, H, head_ranges)])
         self.out_proj = RowParallelWALinear(synthetic_walinear(H, H, g, bias, s + 3, device), rank, world, group, ranges=head_ranges, exchange=exchange)
         if cfg.kind == "opt":
             self.fc1 = col(4, cfg.ffn, ffn_ranges)
             self.ln1 = nn.LayerNorm(H, device=device, dtype=torch.float16)
             self.ln2 = nn.LayerNorm(H, device=device, dtype=torch.float16)
         else:
-            self.gate_proj, self.up_proj = col(4, cfg.ffn, ffn_ranges), col(5, cfg.ffn, ffn_ranges)
+            self.gate_up_proj = fuse_columns([col(4, cfg.ffn, ffn_ranges), col(5, cfg.ffn, ffn_ranges)])
             self.ln1, self.ln2 = RMSNorm(H, cfg.rms_eps, device), RMSNorm(H, cfg.rms_eps, device)
         self.fc2 = RowParallelWALinear(synthetic_walinear(cfg.ffn, H, g, bias, s + 6, device), rank, world, group, ranges=ffn_ranges, exchange=exchange)
         self.k_cache = self.v_cache = None
@@ -115,7 +117,7 @@ class DecoderLayer(nn.Module):
     def forward(self, x, pos0: int, rope=None):
         B, S, H = x.shape
         h = self.ln1(x)
-        q, k, v = self.q_proj(h), self.k_proj(h), self.v_proj(h)
+        q, k, v = self.qkv_proj(h).split(self.local_heads * self.head_dim, dim=-1)
         q = q.view(B, S, self.local_heads, self.head_dim).transpose(1, 2)
         k = k.view(B, S, self.local_heads, self.head_dim).transpose(1, 2)
         v = v.view(B, S, self.local_heads, self.head_dim).transpose(1, 2)
@@ -134,33 +136,35 @@ class DecoderLayer(nn.Module):
             f = torch.relu(self.fc1(h.reshape(1, B * S, H)))           # the reference's FFN sees [1, B*S, H] (:599-606)
             x = x + self.fc2(f).reshape(B, S, H)
         else:
-            f = F.silu(self.gate_proj(h)) * self.up_proj(h)
-            x = x + self.fc2(f)
+            gate, up = self.gate_up_proj(h).chunk(2, dim=-1)
+            x = x + self.fc2(F.silu(gate) * up)
         return x
 
 
-def _layer_forward_static(self, x, pos_t, mask, rope):
+def _norm_args(norm):
+    """(weight, bias, eps, rms) of an nn.LayerNorm or RMSNorm, as quant.add_norm takes them."""
+    if isinstance(norm, RMSNorm):
+        return norm.weight, None, norm.eps, True
+    return norm.weight, norm.bias, norm.eps, False
+
+
+def _layer_forward_static(self, x, delta, pos_t, rope):
     """One-token step with the position held in a device tensor (fixed shapes: capturable in a CUDA graph).
-    Attends over the whole static cache under `mask` (True where position <= current)."""
+    `delta` is the previous block's output still to be added to the residual stream `x` (None for the first
+    layer): the add is fused with the normalisation that follows it.  The fused q/k/v GEMV feeds the decode
+    attention kernel, which also appends to the cache and applies the rotary embedding (`rope` = the full
+    (cos, sin) tables or None).  Returns (x, delta) for the next layer."""
+    from quant import add_norm, decode_attention, silu_mul
     B, S, H = x.shape
-    h = self.ln1(x)
-    q, k, v = self.q_proj(h), self.k_proj(h), self.v_proj(h)
-    q = q.view(B, 1, self.local_heads, self.head_dim).transpose(1, 2)
-    k = k.view(B, 1, self.local_heads, self.head_dim).transpose(1, 2)
-    v = v.view(B, 1, self.local_heads, self.head_dim).transpose(1, 2)
-    if rope is not None:
-        q, k = apply_rope(q, rope[0], rope[1]), apply_rope(k, rope[0], rope[1])
-    self.k_cache.index_copy_(2, pos_t, k)
-    self.v_cache.index_copy_(2, pos_t, v)
-    a = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask)
-    a = a.transpose(1, 2).reshape(B, 1, self.local_heads * self.head_dim)
-    x = x + self.out_proj(a)
-    h = self.ln2(x)
+    x, h = add_norm(x, delta, *_norm_args(self.ln1))
+    qkv = self.qkv_proj(h).view(B, -1)
+    a = decode_attention(qkv, self.k_cache, self.v_cache, pos_t, self.local_heads, rope=rope).view(B, 1, -1)
+    x, h = add_norm(x, self.out_proj(a), *_norm_args(self.ln2))
     if self.cfg.kind == "opt":
-        x = x + self.fc2(torch.relu(self.fc1(h.reshape(1, B, H)))).reshape(B, 1, H)
+        delta = self.fc2(self.fc1(h.reshape(1, B, H), relu=True)).reshape(B, 1, H)
     else:
-        x = x + self.fc2(F.silu(self.gate_proj(h)) * self.up_proj(h))
-    return x
+        delta = self.fc2(silu_mul(self.gate_up_proj(h)))
+    return x, delta
 
 
 DecoderLayer.forward_static = _layer_forward_static
@@ -245,11 +249,13 @@ class Decoder(nn.Module):
         if self.cfg.kind == "opt":
             x = x + self.pos_embed.index_select(0, pos_t + 2)
         else:
-            rope = (self.rope_cos.index_select(0, pos_t), self.rope_sin.index_select(0, pos_t))
-        mask = (arange <= pos_t).view(1, 1, 1, -1)
+            rope = (self.rope_cos, self.rope_sin)
+        from quant import add_norm
+        x, delta = x.contiguous(), None
         for layer in self.layers:
-            x = layer.forward_static(x, pos_t, mask, rope)
-        logits = self.final_norm(x[:, -1]) @ self.lm_head.t()
+            x, delta = layer.forward_static(x, delta, pos_t, rope)
+        _, h = add_norm(x, delta, *_norm_args(self.final_norm))
+        logits = h[:, -1] @ self.lm_head.t()
         if self.world > 1 and self.exchange is not None:
             # each rank's best (logit, vocabulary index) of its shard; ties go to the lowest rank = lowest index
             val, idx = logits.float().max(-1)

@@ -40,15 +40,17 @@ class WALinear(nn.Module):
             self.register_buffer("bias", None)
 
     @torch.no_grad()
-    def forward(self, x):
+    def forward(self, x, relu: bool = False):
         """x fp16 [..., K] -> fp16 [..., N].  The reference requires 3-D input (gemm_quant.cu:73);
-        2-D and >3-D inputs are viewed as [1, tokens, K] here."""
+        2-D and >3-D inputs are viewed as [1, tokens, K] here.  relu=True fuses the ReLU that follows (OPT's fc1)
+        into the kernel epilogue."""
         shape = x.shape
         x3 = x if x.dim() == 3 else x.reshape(1, -1, shape[-1])
         if not x3.is_contiguous():
             x3 = x3.contiguous()
+        extra = {"relu": True} if relu else {}
         y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size,
-                          static_weights=self.static_weights)
+                          static_weights=self.static_weights, **extra)
         return y if x.dim() == 3 else y.reshape(*shape[:-1], self.out_features)
 
     @staticmethod

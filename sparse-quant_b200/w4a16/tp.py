@@ -75,6 +75,26 @@ def _from_buffers(w, zs, b, group_size):
     return lin
 
 
+def fuse_columns(linears):
+    """Several W4A16 linears with the same input (q/k/v; gate/up) -> ONE WALinear whose output is their outputs
+    side by side, built in the packed domain without re-quantising: the `weight` buffers are [K/32][N_i/32][128]
+    tile grids that concatenate along the tile-column axis, `zeros_scales` [K/g, 2N_i] and `bias` [1, N_i] along
+    their columns.  The reference carries the same idea as an unused hook (fuse_w1_w3_s4_k_m8, format.cu:114-120).
+    Accepts WALinear or ColumnParallelWALinear (their local shard); all must share K, group size and bias-ness."""
+    lins = [l.linear if isinstance(l, ColumnParallelWALinear) else l for l in linears]
+    K, g = lins[0].in_features, lins[0].group_size
+    assert all(l.in_features == K and l.group_size == g for l in lins), "fused linears must share K and group size"
+    assert all((l.bias is None) == (lins[0].bias is None) for l in lins), "either all or none of the fused linears carry a bias"
+    w = torch.cat([l.weight.reshape(K // 32, l.out_features // 32, 128) for l in lins], dim=1)
+    N = sum(l.out_features for l in lins)
+    w = w.reshape(K, N // 8).contiguous()
+    zs = torch.cat([l.zeros_scales for l in lins], dim=1).contiguous()
+    b = None if lins[0].bias is None else torch.cat([l.bias for l in lins], dim=1).contiguous()
+    fused = _from_buffers(w, zs, b, g)
+    fused.static_weights = all(l.static_weights for l in lins)
+    return fused
+
+
 class ColumnParallelWALinear(nn.Module):
     """y_local = x @ W[n0:n1]^T (+ b[n0:n1]); the output stays sharded (feeds attention heads or the
     elementwise activation of the FFN)."""
@@ -87,8 +107,8 @@ class ColumnParallelWALinear(nn.Module):
         w, zs, b = shard_column(full.weight, full.zeros_scales, full.bias, self.n0, self.n1)
         self.linear = _from_buffers(w, zs, b, g)
 
-    def forward(self, x):
-        return self.linear(x)
+    def forward(self, x, relu: bool = False):
+        return self.linear(x, relu=relu) if relu else self.linear(x)
 
 
 class PeerExchange:
