@@ -142,6 +142,14 @@ int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_d
                     int tokens, int N, int K, int group_size,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same without the final synchronisation: enqueues copy-in, GEMM and copy-out on `stream` and returns; the
+ * caller synchronises the stream (once for a whole batch of calls) before reading `out_host`.  Host buffers must be
+ * pinned for the copies to be asynchronous. */
+int w4a16_gemm_host_async(const void* x_host, void* out_host, void* x_dev, void* out_dev,
+                    const void* qweight, const void* zeros_scales, const void* bias,
+                    int tokens, int N, int K, int group_size,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
 /*
  * Decode GEMV fused with the all-reduce of a row-parallel linear (tensor parallelism; no counterpart in the
  * reference, which is single-GPU: it stands where a sharded WALinear.forward, qlinear.py:58-72, would be followed
@@ -195,6 +203,8 @@ int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_s
 int w4a16_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, const void* pos,
                            const void* rope_cos, const void* rope_sin, int batch, int heads, int head_dim,
                            int max_len, int qkv_stride, float scale, void* stream);
+/* Tuning hook (tests, benchmarks): CTAs per (head, sequence) splitting the cached positions, 0 = automatic. */
+void w4a16_tune_attention(int split);
 
 /*
  * Residual add fused with the normalisation that follows it, for decode-sized inputs.  Replaces the reference's

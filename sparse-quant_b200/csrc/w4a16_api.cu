@@ -181,9 +181,10 @@ extern "C" int w4a16_gemm(const void* x, const void* qweight, const void* zeros_
                            stream, W4A16_ALGO_AUTO);
 }
 
-extern "C" int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_dev, const void* qweight,
-                               const void* zeros_scales, const void* bias, int tokens, int N, int K, int group_size,
-                               void* workspace, size_t workspace_bytes, void* stream)
+namespace {
+int gemm_host_impl(const void* x_host, void* out_host, void* x_dev, void* out_dev, const void* qweight,
+                   const void* zeros_scales, const void* bias, int tokens, int N, int K, int group_size,
+                   void* workspace, size_t workspace_bytes, void* stream, bool sync)
 {
     if (tokens < 0) return W4A16_ERR_BAD_SHAPE;
     if (tokens == 0) return W4A16_OK;
@@ -195,8 +196,26 @@ extern "C" int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, 
     if (s != W4A16_OK) return s;
     e = cudaMemcpyAsync(out_host, out_dev, (size_t)tokens * N * sizeof(__half), cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) return record_cuda_error(e);
+    if (!sync) return W4A16_OK;
     e = cudaStreamSynchronize(st);
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+}  // namespace
+
+extern "C" int w4a16_gemm_host(const void* x_host, void* out_host, void* x_dev, void* out_dev, const void* qweight,
+                               const void* zeros_scales, const void* bias, int tokens, int N, int K, int group_size,
+                               void* workspace, size_t workspace_bytes, void* stream)
+{
+    return gemm_host_impl(x_host, out_host, x_dev, out_dev, qweight, zeros_scales, bias, tokens, N, K, group_size, workspace,
+                          workspace_bytes, stream, true);
+}
+
+extern "C" int w4a16_gemm_host_async(const void* x_host, void* out_host, void* x_dev, void* out_dev, const void* qweight,
+                                     const void* zeros_scales, const void* bias, int tokens, int N, int K, int group_size,
+                                     void* workspace, size_t workspace_bytes, void* stream)
+{
+    return gemm_host_impl(x_host, out_host, x_dev, out_dev, qweight, zeros_scales, bias, tokens, N, K, group_size, workspace,
+                          workspace_bytes, stream, false);
 }
 
 extern "C" int w4a16_device_error_flag(int* flag)

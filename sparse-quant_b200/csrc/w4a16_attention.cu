@@ -10,11 +10,16 @@
 //   pos  int64 on the device (so that a captured graph can be replayed for every token)
 //   optional rotary tables cos/sin fp16 [positions, D] ("rotate half" convention), applied to q and the new k
 //
-// One CTA per (head, sequence), 256 threads.  Scores: one lane per cached position, 16-byte loads along the key
-// row, fp32 dot product against q held in shared memory.  Softmax in fp32 over the scores kept in shared memory.
+// One CTA - or a cluster of up to 8 splitting the positions - per (head, sequence), 256 threads.  Scores: D/8
+// adjacent lanes per cached key row (coalesced 16-byte loads, eight in flight per lane), q in registers, shuffle
+// reduction, fp32.  Softmax in fp32 over the scores kept in shared memory.
 // P.V: a thread owns eight adjacent output dims (16-byte loads) and every G-th position, eight loads in flight;
 // the G partial sums meet in shared memory.  Bound: HBM (the cache is read once: 2 * (pos+1) * D * 2 bytes per CTA).
+#include <cooperative_groups.h>
+
 #include "w4a16_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace w4a16 {
 namespace {
@@ -47,31 +52,50 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
+// fp32 load from the shared memory of CTA `rank` of this cluster
+__device__ __forceinline__ float ld_cluster(const float* local, unsigned rank)
+{
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// grid = (heads, batch, S); the S CTAs of a thread-block cluster split the cached positions of one (head, sequence)
+// evenly, each produces (max, sum, unnormalised output) of its range, and CTA 0 combines them through distributed
+// shared memory.  S is fixed by the host (it cannot know the position), so that few (head, sequence) pairs - the
+// head-sharded case under tensor parallelism - still fill the machine and keep the per-CTA chain of dependent
+// memory round trips short.
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const AttnParams p)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kCols = D / 8, kGroups = kAttnThreads / kCols;          // P.V thread layout
     float* q_s = reinterpret_cast<float*>(smem_raw);                        // [D]
-    float* red = q_s + D;                                                   // [kGroups][D] partial outputs; also warp scratch
+    float* part = q_s + D;                                                  // [D] this CTA's unnormalised output, then [2]: max, sum
+    float* red = part + D + 8;                                              // [kGroups][D] partial outputs; also warp scratch
     float* sc = red + kGroups * D;                                          // [max_len] scores / probabilities
     const int head = blockIdx.x, b = blockIdx.y;
+    const int S = gridDim.z, rank = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // a following kernel launched with programmatic stream serialization (the decode GEMV prefetching its static
     // weights) may start its preamble as soon as every CTA of this grid is running
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long cur_ll = *p.pos;
     if (cur_ll < 0 || cur_ll >= p.max_len) {                                // position outside the cache: refuse
-        if (tid == 0) atomicExch(p.error, 3);
+        if (tid == 0) atomicExch(p.error, 3);                               // (uniform over the cluster: nobody waits)
         return;
     }
     const int cur = (int)cur_ll, n = cur + 1;
+    const int t_lo = (int)((long long)n * rank / S), t_hi = (int)((long long)n * (rank + 1) / S);   // the last rank owns `cur`
     const size_t row0 = ((size_t)b * p.heads + head) * p.max_len;          // first cache row of this (sequence, head)
     const __half* qrow = p.qkv + (size_t)b * p.qkv_stride + head * D;
     const __half* krow = qrow + p.heads * D;
     const __half* vrow = krow + p.heads * D;
 
-    // new token: rotary embedding on q and k, k/v appended to the cache, q (scaled) to shared memory
+    // new token: rotary embedding on q and k, k/v appended to the cache (by the rank that reads it back), q
+    // (scaled) to shared memory
     if (tid < D) {
         const int i = tid, j = i < D / 2 ? i + D / 2 : i - D / 2;
         float q = __half2float(qrow[i]), k = __half2float(krow[i]);
@@ -83,36 +107,49 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             k = k * c + sign * ko * s;
         }
         q_s[i] = q * p.scale;
-        p.k_cache[(row0 + cur) * D + i] = __float2half_rn(k);
-        p.v_cache[(row0 + cur) * D + i] = vrow[i];
+        if (rank == S - 1) {
+            p.k_cache[(row0 + cur) * D + i] = __float2half_rn(k);
+            p.v_cache[(row0 + cur) * D + i] = vrow[i];
+        }
     }
     __syncthreads();                                                        // the appended row is visible to the CTA
 
-    // scores: lane <-> position, 32 positions per warp pass
-    float lmax = -INFINITY;
-    for (int t0 = warp * 32; t0 < n; t0 += (kAttnThreads / 32) * 32) {
-        const int t = t0 + lane;
-        if (t < n) {
-            const uint4* kr = reinterpret_cast<const uint4*>(p.k_cache + (row0 + t) * D);
-            uint4 kv[D / 8];
+    // scores: D/8 adjacent lanes read one key row with 16-byte loads (a warp load covers 32/(D/8) whole rows: fully
+    // coalesced), eight row groups in flight per lane; each lane multiplies its 8 dims by q from registers and the
+    // row's lanes add up with shuffles
+    constexpr int kLPR = D / 8, kRPI = 32 / kLPR, kU = 8;                   // lanes per row, rows per warp load, loads in flight
+    const int sub = lane / kLPR, li = lane % kLPR;
+    float qreg[8];
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) kv[c] = kr[c];
+    for (int e = 0; e < 8; ++e) qreg[e] = q_s[li * 8 + e];
+    float lmax = -INFINITY;
+    for (int base = t_lo + warp * (kRPI * kU); base < t_hi; base += (kAttnThreads / 32) * (kRPI * kU)) {
+        uint4 kv[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int t = base + u * kRPI + sub;
+            kv[u] = t < t_hi ? *reinterpret_cast<const uint4*>(p.k_cache + (row0 + t) * D + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const __half2* h = reinterpret_cast<const __half2*>(&kv[u]);
             float dot = 0.f;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
-                const __half2* h = reinterpret_cast<const __half2*>(&kv[c]);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __half22float2(h[e]);
-                    dot = fmaf(f.x, q_s[c * 8 + 2 * e], dot);
-                    dot = fmaf(f.y, q_s[c * 8 + 2 * e + 1], dot);
-                }
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                dot = fmaf(f.x, qreg[2 * e], dot);
+                dot = fmaf(f.y, qreg[2 * e + 1], dot);
             }
-            sc[t] = dot;
-            lmax = fmaxf(lmax, dot);
+#pragma unroll
+            for (int o = kLPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const int t = base + u * kRPI + sub;
+            if (li == 0 && t < t_hi) {
+                sc[t - t_lo] = dot;
+                lmax = fmaxf(lmax, dot);
+            }
         }
     }
-    // softmax over sc[0..n)
+    // softmax numerators over this CTA's range, relative to its own maximum
     lmax = warp_max(lmax);
     if (lane == 0) red[warp] = lmax;
     __syncthreads();
@@ -120,8 +157,9 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 #pragma unroll
     for (int w = 1; w < kAttnThreads / 32; ++w) gmax = fmaxf(gmax, red[w]);
     __syncthreads();                                                        // red[] is reused below
+    const int cnt = t_hi - t_lo;
     float lsum = 0.f;
-    for (int t = tid; t < n; t += kAttnThreads) {
+    for (int t = tid; t < cnt; t += kAttnThreads) {
         const float e = __expf(sc[t] - gmax);
         sc[t] = e;
         lsum += e;
@@ -132,14 +170,13 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     float gsum = 0.f;
 #pragma unroll
     for (int w = 0; w < kAttnThreads / 32; ++w) gsum += red[w];
-    const float inv = 1.f / gsum;
     __syncthreads();
 
-    // out = P . V: thread (group, col) adds positions group, group + G, ... for dims 8 col .. 8 col + 7
+    // P . V: thread (group, col) adds positions group, group + G, ... for dims 8 col .. 8 col + 7
     {
         const int col = tid % kCols, grp = tid / kCols;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const __half* vbase = p.v_cache + row0 * D + col * 8;
+        const __half* vbase = p.v_cache + (row0 + t_lo) * D + col * 8;
         constexpr int kUnroll = 8;
         auto add_row = [&](const uint4& v, float pr) {
             const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -151,13 +188,13 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             }
         };
         // whole chunks of kUnroll positions, the last one predicated: all loads of a chunk are in flight together
-        for (int t = grp; t < n; t += kUnroll * kGroups) {
+        for (int t = grp; t < cnt; t += kUnroll * kGroups) {
             uint4 v[kUnroll];
             float pr[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 const int tu = t + u * kGroups;
-                const bool in = tu < n;
+                const bool in = tu < cnt;
                 v[u] = in ? *reinterpret_cast<const uint4*>(vbase + (size_t)tu * D) : make_uint4(0, 0, 0, 0);
                 pr[u] = in ? sc[tu] : 0.f;
             }
@@ -168,19 +205,43 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         *reinterpret_cast<float4*>(red + grp * D + col * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __syncthreads();
+    float mine = 0.f;
     if (tid < D) {
-        float s = 0.f;
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g) s += red[g * D + tid];
-        p.out[((size_t)b * p.heads + head) * D + tid] = __float2half_rn(s * inv);
+        for (int g = 0; g < kGroups; ++g) mine += red[g * D + tid];
     }
+    __half* dst = p.out + ((size_t)b * p.heads + head) * D;
+    if (S == 1) {
+        if (tid < D) dst[tid] = __float2half_rn(mine / gsum);
+        return;
+    }
+    // combine the ranks: out = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M); a rank without positions has
+    // m_r = -inf, l_r = 0 and drops out
+    if (tid < D) part[tid] = mine;
+    if (tid == 0) { part[D] = gmax; part[D + 1] = gsum; }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (rank == 0 && tid < D) {
+        float M = -INFINITY;
+        for (int r = 0; r < S; ++r) M = fmaxf(M, ld_cluster(part + D, (unsigned)r));
+        float num = 0.f, den = 0.f;
+        for (int r = 0; r < S; ++r) {
+            const float w = __expf(ld_cluster(part + D, (unsigned)r) - M);
+            num = fmaf(ld_cluster(part + tid, (unsigned)r), w, num);
+            den = fmaf(ld_cluster(part + D + 1, (unsigned)r), w, den);
+        }
+        dst[tid] = __float2half_rn(num / den);
+    }
+    cluster.sync();                                                         // rank 0 may still be reading this CTA's part[]
 }
+
+int g_force_attn_split = 0;
 
 template <int D>
 int launch_attention(const AttnParams& p, int batch, cudaStream_t st)
 {
     constexpr int kGroups = kAttnThreads / (D / 8);
-    const size_t smem = sizeof(float) * ((size_t)D + (size_t)kGroups * D + p.max_len);
+    const size_t smem = sizeof(float) * ((size_t)2 * D + 8 + (size_t)kGroups * D + p.max_len);
     if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
     static int configured[64] = {0};   // benign race: the attribute call is idempotent
     int dev = 0;
@@ -191,9 +252,24 @@ int launch_attention(const AttnParams& p, int batch, cudaStream_t st)
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev < 64) configured[dev] = (int)smem;
     }
-    decode_attention_kernel<D><<<dim3(p.heads, batch), kAttnThreads, smem, st>>>(p);
+    // context split: enough CTAs for two per SM, at most 8 per (head, sequence), not more than one per 32 cache rows
+    int split = 1;
+    while (split < 8 && (long long)p.heads * batch * split < 2 * 148 && split * 2 * 32 <= p.max_len) split <<= 1;
+    if (g_force_attn_split) split = g_force_attn_split;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.heads, batch, split);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = split;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, decode_attention_kernel<D>, p);
     count_launch();
-    e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
 
@@ -201,6 +277,9 @@ int launch_attention(const AttnParams& p, int batch, cudaStream_t st)
 }  // namespace w4a16
 
 using namespace w4a16;
+
+// Tuning hook for tests and benchmarks: CTAs per (head, sequence), 0 = automatic.  Not part of the drop-in surface.
+extern "C" void w4a16_tune_attention(int split) { w4a16::g_force_attn_split = (split == 1 || split == 2 || split == 4 || split == 8) ? split : 0; }
 
 extern "C" int w4a16_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, const void* pos,
                                       const void* rope_cos, const void* rope_sin, int batch, int heads, int head_dim,

@@ -50,6 +50,7 @@ C_ABI = {
     "w4a16_gemm_allreduce": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz,
                                    _vp, ctypes.c_uint]),
     "w4a16_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.c_float, _vp]),
+    "w4a16_tune_attention": (None, [_ci]),
     "w4a16_add_norm": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float, _ci, _vp]),
     "w4a16_silu_mul": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_gemm_static_scratch": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp]),
@@ -59,6 +60,7 @@ C_ABI = {
     "w4a16_convert_ours_to_awq": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_convert_awq_to_lmdeploy": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_gemm_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
+    "w4a16_gemm_host_async": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_launch_count": (ctypes.c_ulonglong, []),
     "w4a16_version": (_ci, []),
     "w4a16_device_error_flag": (_ci, [ctypes.POINTER(_ci)]),

@@ -122,3 +122,18 @@ def test_silu_mul_and_relu_epilogue():
         plain = quant.gemm_awq_bias(x, qw, zs, bias, 512, 128, algo=algo)
         fused = quant.gemm_awq_bias(x, qw, zs, bias, 512, 128, algo=algo, relu=True)
         assert torch.equal(fused, torch.relu(plain)) and (plain < 0).any()
+
+
+def test_decode_attention_context_split_over_a_cluster():
+    """The positions of one (head, sequence) split over 2/4/8 CTAs of a cluster and recombined: same tolerance as
+    the single-CTA form, including positions smaller than the split (ranks with nothing to do)."""
+    import quant
+    lib = quant.load_library()
+    try:
+        for split in (1, 2, 4, 8):
+            lib.w4a16_tune_attention(split)
+            for pos in (0, 2, 5, 63, 64, 500, 639):
+                _case(B=2, H=3, D=128, L=640, pos=pos, rope=(pos % 2 == 0), seed=pos + split)
+            _case(B=2, H=3, D=64, L=320, pos=319, rope=True, seed=split)
+    finally:
+        lib.w4a16_tune_attention(0)

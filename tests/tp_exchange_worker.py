@@ -56,10 +56,11 @@ def main():
 
     # 3. a small decoder: the graph-replayed TP step (no library collective inside) against the same step run
     #    eagerly, and logits against the NCCL route
+    hidden = max(512, 128 * world)           # every rank's K shard of out_proj must hold whole quantisation groups
     for kind in ("opt", "llama"):
-        cfg = (DecoderConfig("opt", layers=2, hidden=512, heads=8, ffn=2048, vocab=1024, group_size=128, max_positions=128)
+        cfg = (DecoderConfig("opt", layers=2, hidden=hidden, heads=8, ffn=2048, vocab=1024, group_size=128, max_positions=128)
                if kind == "opt" else
-               DecoderConfig("llama", layers=2, hidden=512, heads=8, ffn=1344, vocab=1024, group_size=64, max_positions=128))
+               DecoderConfig("llama", layers=2, hidden=hidden, heads=8, ffn=1344, vocab=1024, group_size=64, max_positions=128))
         ids = torch.randint(0, cfg.vocab, (4, 40), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
         model = Decoder(cfg, rank, world, None, dev, seed=5, exchange=ex).mark_static()
         plain = Decoder(cfg, rank, world, None, dev, seed=5).mark_static()
