@@ -214,6 +214,8 @@ def main():
     ap.add_argument("--single", default=None, metavar="K,N,M[,ALGO[,REPS]]",
                     help="only launch one shape REPS times over 4 rotating weight sets and exit (driver for ncu captures); "
                          "ALGO 0 auto, 1 skinny, 2 tcgen05")
+    ap.add_argument("--single-attention", default=None, metavar="B,H,D,L,POS[,REPS]",
+                    help="only launch the decode attention kernel REPS times over 4 rotating caches and exit (driver for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -222,6 +224,9 @@ def main():
         return
     if args.single:
         run_single(args.single)
+        return
+    if args.single_attention:
+        run_single_attention(args.single_attention)
         return
     if args.workload != "decode-sweep":
         run_model(args)
@@ -483,6 +488,27 @@ def run_single(spec):
             raise RuntimeError(lib.w4a16_status_str(r).decode())
     torch.cuda.synchronize()
     print(json.dumps({"single": spec, "mean_abs_out": float(o.float().abs().mean())}))
+
+
+def run_single_attention(spec):
+    """A handful of launches of the decode attention kernel on one shape, for profiler captures: B,H,D,L,POS[,REPS]
+    (the caches of 4 rotating layers are larger than L2 for the model-sized shapes)."""
+    import quant
+    v = [int(t) for t in spec.split(",")]
+    B, H, D, L, pos = v[:5]
+    reps = v[5] if len(v) > 5 else 6
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    caches = [(torch.randn(B, H, L, D, device=dev, dtype=torch.float16), torch.randn(B, H, L, D, device=dev, dtype=torch.float16))
+              for _ in range(4)]
+    qkv = torch.randn(B, 3 * H * D, device=dev, dtype=torch.float16)
+    pos_t = torch.tensor([pos], device=dev)
+    for i in range(reps):
+        kc, vc = caches[i % 4]
+        out = quant.decode_attention(qkv, kc, vc, pos_t, H)
+    torch.cuda.synchronize()
+    print(json.dumps({"single_attention": spec, "mean_abs_out": float(out.float().abs().mean()),
+                      "algorithmic_bytes": 2 * B * H * (pos + 1) * D * 2}))
 
 
 def time_calls(fn, stream, iters, warm=5):

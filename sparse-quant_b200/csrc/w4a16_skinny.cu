@@ -558,6 +558,49 @@ int stage_bytes(int rows, int K, int splits, int kUnitK, int tg, int g)
     return kHeaderBytes + xs_bytes(rows, K, splits, kUnitK) + xsum_bytes(tg, K, splits, kUnitK, g);
 }
 
+// How many clusters of `sp` CTAs of this kernel the current device runs at once (the kernel takes a whole SM per CTA,
+// so this is a property of how the SMs are grouped into GPCs, not of the problem).  Cached per device and size.
+template <int TG, int G>
+int max_clusters_instance(int sp)
+{
+    static int cache[64][9] = {};      // benign race: the query is idempotent
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148 / sp;
+    if (cache[dev][sp]) return cache[dev][sp];
+    int n = 0;
+    const int smem = 200 * 1024;
+    if (cudaFuncSetAttribute(skinny_kernel<TG, G, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, sp, 1);
+        cfg.blockDim = dim3(512);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = sp;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, skinny_kernel<TG, G, 16>, &cfg) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+    } else {
+        (void)cudaGetLastError();
+    }
+    if (n <= 0) n = 148 / sp;          // query unavailable: assume perfect packing
+    cache[dev][sp] = n;
+    return n;
+}
+
+int max_clusters(int tg, int g, int sp)
+{
+    if (sp <= 1) return 148;
+    if (tg != 4) return 148 / sp;
+    switch (g) {
+        case 128: return max_clusters_instance<4, 128>(sp);
+        case 64:  return max_clusters_instance<4, 64>(sp);
+        default:  return max_clusters_instance<4, 32>(sp);
+    }
+}
+
 Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
 {
     Config c;
@@ -582,6 +625,27 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
     // every K slice of a CTA should own at least one 128-k unit
     while (c.wn < kWarps && (kWarps / c.wn) * c.splits > units) c.wn <<= 1;
     if (g_force_wn) c.wn = g_force_wn;
+    if (c.tg == 4 && !g_force_wn && !g_force_splits) {
+        // 17..32 tokens: the staged activations crowd out the rings, and power-of-two clusters often leave a third
+        // of the SMs idle (e.g. 384 out-feature tiles: 48 x 2 CTAs).  Search all (tiles per CTA, cluster size <= 8)
+        // for the most CTAs within one wave, weighted by how deep a ring still fits; ties go to the smaller cluster.
+        double best = -1.0;
+        for (int wn = 1; wn <= kWarps; wn <<= 1) {
+            for (int sp = 1; sp <= 8; ++sp) {
+                if (sp > units) break;
+                const long long ctas = (long long)((n_tiles + wn - 1) / wn) * sp;
+                if (ctas > 148 || ctas / sp > max_clusters(c.tg, g, sp)) continue;      // one wave, as the device packs clusters
+                const int room = kSmemBudget - stage_bytes(rows, K, sp, kUnitK, c.tg, g);
+                int depth = room / ring1;
+                if (depth < 2) continue;
+                if (depth > max_depth_for(c.tg)) depth = max_depth_for(c.tg);
+                if (g_force_depth && g_force_depth < depth) depth = g_force_depth;
+                const double score = (double)ctas * (depth >= 4 ? 1.0 : depth == 3 ? 0.9 : 0.7) - 0.01 * sp;
+                if (score > best) { best = score; c.wn = wn; c.splits = sp; c.depth = depth; }
+            }
+        }
+        if (best < 0) c.splits = 8;      // nothing fits: the caller falls back to two passes of 16 tokens
+    }
     return c;
 }
 
@@ -666,7 +730,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     const int kWarps = c.warps;
     if (c.wn != 1 && c.wn != 2 && c.wn != 4 && c.wn != 8 && c.wn != 16 && c.wn != 32) return W4A16_ERR_BAD_ALGO;
     if (c.wn > kWarps) return W4A16_ERR_BAD_ALGO;
-    if (c.splits != 1 && c.splits != 2 && c.splits != 4 && c.splits != 8) return W4A16_ERR_BAD_ALGO;
+    if (c.splits < 1 || c.splits > 8) return W4A16_ERR_BAD_ALGO;
 
     SkinnyParams p;
     p.x = a.x; p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out;

@@ -44,6 +44,14 @@ def test_skinny_small_tokens(N, K, g, M):
     run(M, N, K, g, algo=1, bias=(M % 2 == 0))
 
 
+@pytest.mark.parametrize("N,K,g", [(1536, 4096, 64), (2752, 4096, 64), (512, 11008, 64), (1024, 16384, 128)])
+@pytest.mark.parametrize("M", [24, 32])
+def test_decode_kernel_17_to_32_tokens_cluster_shapes(M, N, K, g):
+    """17..32 tokens: the launch shape is searched over cluster sizes 1..8 (odd ones included) or falls back to
+    two 16-token passes; these shapes hit 3-, 7/8-CTA clusters and the fallback."""
+    run(M, N, K, g, algo=1, bias=True)
+
+
 @pytest.mark.parametrize("M", [33, 100, 257])
 def test_skinny_many_tokens_fallback(M):
     run(M, 256, 512, 128, algo=1, bias=True)
