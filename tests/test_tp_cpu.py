@@ -140,3 +140,20 @@ def test_failing_rank_surfaces_as_error_on_its_peer():
     res = _run_tp(256, 128, 128, fail_rank=1)
     assert res[1][0] == "error" and "injected failure" in res[1][1]
     assert res[0][0] == "error", "rank 0 must see its collective fail (timeout / peer gone), not hang"
+
+
+def test_fused_sibling_linears_are_the_concatenation_of_their_dequantised_weights():
+    """fuse_columns builds q|k|v (or gate|up) in the packed domain: dequantising the fused buffers must give exactly
+    the dequantised siblings stacked along the out-feature axis, bias included."""
+    from w4a16.tp import fuse_columns
+    K, g = 256, 64
+    parts = [_packed_linear(n, K, g, seed=20 + i) for i, n in enumerate((96, 32, 160))]
+    fused = fuse_columns(parts)
+    assert fused.out_features == 288 and fused.in_features == K and fused.group_size == g
+    got = oracle.dequant(fused.weight.numpy().view(np.uint32), fused.zeros_scales.numpy().view(np.uint16), K, 288, g)
+    want = np.concatenate([oracle.dequant(p.weight.numpy().view(np.uint32), p.zeros_scales.numpy().view(np.uint16), K, p.out_features, g)
+                           for p in parts], axis=0)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert torch.equal(fused.bias, torch.cat([p.bias for p in parts], dim=1))
+    with pytest.raises(AssertionError):
+        fuse_columns([parts[0], _packed_linear(32, 128, g, seed=1)])          # different K
