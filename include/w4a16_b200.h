@@ -205,6 +205,9 @@ int w4a16_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* 
                            int max_len, int qkv_stride, float scale, void* stream);
 /* Tuning hook (tests, benchmarks): CTAs per (head, sequence) splitting the cached positions, 0 = automatic. */
 void w4a16_tune_attention(int split);
+/* Tuning hook: 1 launches the small decode-step kernels with programmatic stream serialization, 0 (default) in plain
+ * stream order. */
+void w4a16_tune_aux_launch(int programmatic);
 
 /*
  * Residual add fused with the normalisation that follows it, for decode-sized inputs.  Replaces the reference's

@@ -19,6 +19,9 @@ int record_cuda_error(cudaError_t e)
     return W4A16_ERR_CUDA;
 }
 
+namespace { std::atomic<int> g_aux_programmatic{0}; }
+bool aux_programmatic_launch() { return g_aux_programmatic.load(std::memory_order_relaxed) != 0; }
+
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // Allocated once per device (first use; outside stream capture), never freed, only ever set to 1.
@@ -232,3 +235,7 @@ extern "C" void w4a16_tune_skinny(int wn, int splits) { skinny_force_config(wn, 
 // Debug aid: device buffer [ctas][16 warps][8] receiving %globaltimer stamps of the skinny kernel's phases (NULL = off).
 extern "C" void w4a16_debug_skinny_timeline(void* buf) { skinny_set_timeline((unsigned long long*)buf); }
 extern "C" void w4a16_tune_tc(int tile_tokens, int split_k) { tc_force_config(tile_tokens, split_k); }
+// 1: the small decode-step kernels (attention, add+norm, SwiGLU product, exchange all-gather) are launched with
+// programmatic stream serialization; 0 (default): plain stream order - measured faster (OPT-6.7B-shaped step 1.8 %,
+// LLaMA-2-7B-shaped step 7 %): their early-resident CTAs only compete with the kernel they wait for.
+extern "C" void w4a16_tune_aux_launch(int programmatic) { g_aux_programmatic.store(programmatic ? 1 : 0, std::memory_order_relaxed); }

@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     // a following kernel launched with programmatic stream serialization (the decode GEMV prefetching its static
     // weights) may start its preamble as soon as every CTA of this grid is running
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // launched early itself: q/k/v and the position come from earlier work
     const long long cur_ll = *p.pos;
     if (cur_ll < 0 || cur_ll >= p.max_len) {                                // position outside the cache: refuse
         if (tid == 0) atomicExch(p.error, 3);                               // (uniform over the cluster: nobody waits)
@@ -261,13 +262,15 @@ int launch_attention(const AttnParams& p, int batch, cudaStream_t st)
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = split;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = aux_programmatic_launch() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, decode_attention_kernel<D>, p);
     count_launch();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);

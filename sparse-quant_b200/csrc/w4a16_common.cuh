@@ -166,6 +166,26 @@ struct GemmArgs {
     const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
 };
 
+// Launch, optionally with programmatic stream serialization (the grid may then be scheduled while the previous
+// kernel of the stream drains).  Only for kernels that execute griddepcontrol.wait before they touch anything the
+// stream's earlier work produces.
+bool aux_programmatic_launch();                  // tuning switch (w4a16_tune_aux_launch), default off
+template <typename... KArgs, typename... Args>
+cudaError_t launch_after_previous(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = aux_programmatic_launch() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 int  record_cuda_error(cudaError_t e);          // returns W4A16_ERR_CUDA, remembers e
 void count_launch(unsigned n = 1);
 int* device_error_word();

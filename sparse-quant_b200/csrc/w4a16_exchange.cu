@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherPar
 {
     ExchangeHeader* hdr = reinterpret_cast<ExchangeHeader*>(p.self);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&hdr->epoch);
     const unsigned half_sel = epoch & 1u, tag = epoch + 1u;
     for (int i = threadIdx.x; i < p.words; i += blockDim.x) {
@@ -197,8 +198,7 @@ extern "C" int w4a16_exchange_allgather(const void* in, void* out, int words, vo
     p.error = device_error_word();
     if (!p.error) return W4A16_ERR_CUDA;
     p.words = words; p.world = world; p.rank = rank; p.capacity = (long long)capacity_elems;
-    exchange_allgather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p);
+    cudaError_t e = launch_after_previous(exchange_allgather_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, p);
     count_launch();
-    cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }

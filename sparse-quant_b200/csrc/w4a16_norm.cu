@@ -46,8 +46,10 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
 {
     __shared__ float scratch[kNormThreads / 32];
     // lets a following kernel launched with programmatic stream serialization (the decode GEMV) start its
-    // weight prefetch while these few CTAs run
+    // weight prefetch while these few CTAs run; this kernel itself is launched the same way and must not read its
+    // inputs before the previous grid has completed
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t row = (size_t)blockIdx.x * p.cols;
     const int nvec = p.cols / 8;
     float v[kNormMaxVec][8];
@@ -116,6 +118,7 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* in, __half* out, int n, int total_vec)
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int nvec = n / 8;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += gridDim.x * blockDim.x) {
         const int r = i / nvec, c = i - r * nvec;
@@ -146,9 +149,9 @@ extern "C" int w4a16_silu_mul(const void* gate_up, void* out, int rows, int n, v
     if (((uintptr_t)gate_up & 15) || ((uintptr_t)out & 15)) return W4A16_ERR_MISALIGNED;
     const int total_vec = rows * (n / 8);
     const int blocks = (total_vec + 255) / 256 < 592 ? (total_vec + 255) / 256 : 592;
-    silu_mul_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)gate_up, (__half*)out, n, total_vec);
+    cudaError_t e = launch_after_previous(silu_mul_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __half*)gate_up,
+                                          (__half*)out, n, total_vec);
     count_launch();
-    cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
 
@@ -164,8 +167,7 @@ extern "C" int w4a16_add_norm(const void* x, const void* delta, void* x_out, voi
     NormParams p;
     p.x = (const __half*)x; p.delta = (const __half*)delta; p.x_out = (__half*)x_out; p.h_out = (__half*)h_out;
     p.weight = (const __half*)weight; p.bias = (const __half*)bias; p.cols = cols; p.eps = eps; p.rms = rms ? 1 : 0;
-    add_norm_kernel<<<rows, kNormThreads, 0, (cudaStream_t)stream>>>(p);
+    cudaError_t e = launch_after_previous(add_norm_kernel, dim3(rows), dim3(kNormThreads), 0, (cudaStream_t)stream, p);
     count_launch();
-    cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }

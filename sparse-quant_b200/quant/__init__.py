@@ -51,6 +51,7 @@ C_ABI = {
                                    _vp, ctypes.c_uint]),
     "w4a16_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.c_float, _vp]),
     "w4a16_tune_attention": (None, [_ci]),
+    "w4a16_tune_aux_launch": (None, [_ci]),
     "w4a16_add_norm": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float, _ci, _vp]),
     "w4a16_silu_mul": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_gemm_static_scratch": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp]),

@@ -112,8 +112,10 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--gpu", action="store_true")
-    ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out"))
+    ap.add_argument("--reference", default=os.environ.get("W4A16_REFERENCE", "/root/reference"),
+                    help="checkout of the reference project (CPU stage only)")
+    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"),
+                    help="directory that receives golden_reference_cuda.npz (GPU stage)")
     a = ap.parse_args()
     if a.cpu:
         cpu_stage(a.reference)
