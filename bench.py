@@ -88,18 +88,25 @@ class ClockSampler:
             self.max_mhz = None
         self.t = threading.Thread(target=self._run, daemon=True)
 
-    def _run(self):
+    def poll(self):
+        """One sample, taken by the caller's thread (the launching thread calls this right after it has enqueued the
+        timed work, so that even a region of a few milliseconds has a sample from inside it)."""
+        if not self.ok:
+            return
         nv = self.nv
-        while not self.stop:
+        try:
+            mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
             try:
-                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
-                try:
-                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
-                except Exception:
-                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                self.samples.append((time.perf_counter(), mhz, reasons))
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
             except Exception:
-                pass
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            self.samples.append((time.perf_counter(), mhz, reasons))
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self.stop:
+            self.poll()
             time.sleep(0.002)
 
     def start(self):
@@ -352,6 +359,7 @@ def main():
         for _ in range(args.steps):
             run_step()
         e1.record(stream)
+    sampler.poll()
     barrier()
     check_exchange("timed region")
     note("timed region done")
