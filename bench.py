@@ -201,6 +201,26 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+def make_exchange(capacity, dev, dist):
+    """Peer-memory exchange buffers for the fused row-parallel sum, or None when they cannot be set up on this box
+    (no peer access / IPC between the ranks): the ranks agree on the outcome, and the caller then falls back to the
+    NCCL all-reduce with stream-ordered launches."""
+    from w4a16.tp import PeerExchange
+    ex, ok = None, 1
+    try:
+        ex = PeerExchange(capacity, device=dev)
+    except Exception as e:                                    # noqa: BLE001
+        print(f"[bench] peer exchange set-up failed on rank {dist.get_rank()}: {e}", file=sys.stderr, flush=True)
+        ok = 0
+    flag = torch.tensor([ok], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 1:
+        return ex
+    if ex is not None:
+        ex.close()
+    return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,9 +295,8 @@ def main():
 
     exchange = None
     if world > 1 and args.reduce == "fused":
-        from w4a16.tp import PeerExchange
-        exchange = PeerExchange(max(DECODE_M) * max(N for _, N in DECODE_SHAPES), device=dev)
-        note("peer exchange buffers mapped")
+        exchange = make_exchange(max(DECODE_M) * max(N for _, N in DECODE_SHAPES), dev, dist)
+        note("peer exchange buffers mapped" if exchange is not None else "peer exchange unavailable: NCCL all-reduce instead")
 
     weights = {}
     for si, (K, N) in enumerate(DECODE_SHAPES):
@@ -312,6 +331,8 @@ def main():
     collectives_per_step = sum(1 for (M, K, N, s) in calls if local_shape(K, N)[2])
 
     # one eager pass (per-device attribute set-up happens here, outside capture), then capture the step
+    if dist is not None:
+        dist.barrier()                      # ranks enter the first exchange together
     with torch.cuda.stream(stream):
         for c in calls:
             launch(*c, sp)
@@ -434,8 +455,7 @@ def run_model(args):
         cfg.layers = args.layers
     exchange = None
     if world > 1 and args.reduce == "fused":
-        from w4a16.tp import PeerExchange
-        exchange = PeerExchange(32 * cfg.hidden, device=dev)
+        exchange = make_exchange(32 * cfg.hidden, dev, dist)
     model = Decoder(cfg, rank, world, None, dev, seed=1234, exchange=exchange).mark_static()
     ids = torch.randint(0, cfg.vocab, (batch, prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(7))
     steps, warm = max(1, min(args.steps, 5)), 1

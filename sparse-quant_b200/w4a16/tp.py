@@ -133,25 +133,44 @@ class PeerExchange:
         self.device = torch.device(device if device is not None else torch.cuda.current_device())
         self.buffers = (ctypes.c_void_p * 8)()
         self._opened = []
+        self._own = None
         with torch.cuda.device(self.device):
-            own = ctypes.c_void_p()
-            quant._check(self.lib.w4a16_exchange_alloc(self.world, self.capacity, ctypes.byref(own)), "exchange_alloc")
-            self._own = own
-            self.buffers[self.rank] = own.value
+            # Every rank walks through all collective steps whatever happens locally, and the ranks agree on the
+            # outcome at the end (which is also the barrier before anyone's first call): a rank that cannot allocate
+            # or map must not leave its peers waiting in a collective.
+            err = None
+            handle = (ctypes.c_ubyte * 64)()
+            try:
+                own = ctypes.c_void_p()
+                quant._check(self.lib.w4a16_exchange_alloc(self.world, self.capacity, ctypes.byref(own)), "exchange_alloc")
+                self._own = own
+                self.buffers[self.rank] = own.value
+                if self.world > 1:
+                    quant._check(self.lib.w4a16_exchange_export(own, handle), "exchange_export")
+            except Exception as e:                                   # noqa: BLE001
+                err = e
             if self.world > 1:
-                handle = (ctypes.c_ubyte * 64)()
-                quant._check(self.lib.w4a16_exchange_export(own, handle), "exchange_export")
                 handles = [None] * self.world
                 dist.all_gather_object(handles, bytes(handle), group=group)
-                for r, h in enumerate(handles):
-                    if r == self.rank:
-                        continue
-                    peer = ctypes.c_void_p()
-                    raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-                    quant._check(self.lib.w4a16_exchange_open(raw, ctypes.byref(peer)), "exchange_open")
-                    self._opened.append(peer)
-                    self.buffers[r] = peer.value
-                dist.barrier(group=group)          # every buffer is zeroed and mapped before anyone's first call
+                if err is None:
+                    try:
+                        for r, h in enumerate(handles):
+                            if r == self.rank:
+                                continue
+                            peer = ctypes.c_void_p()
+                            raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                            quant._check(self.lib.w4a16_exchange_open(raw, ctypes.byref(peer)), "exchange_open")
+                            self._opened.append(peer)
+                            self.buffers[r] = peer.value
+                    except Exception as e:                           # noqa: BLE001
+                        err = e
+                ok = torch.tensor([0 if err is not None else 1], device=self.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0:
+                    self.close()
+                    raise RuntimeError(f"peer exchange set-up failed on at least one rank (this rank: {err})")
+            elif err is not None:
+                raise err
 
     def allgather(self, t: torch.Tensor) -> torch.Tensor:
         """t: contiguous CUDA tensor of a 4-byte dtype with at most `capacity` elements, same shape on every rank
