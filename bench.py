@@ -188,7 +188,7 @@ def run_reference(args):
               sample=f"{args.steps} step(s), each one pass of the K=4096 N=4096 M=16 call (dequantise in C/OpenMP + torch fp32 matmul)")
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16xs4->f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference path (the reference ships no CPU code for it); "
                                                  "each step is a bounded sample: one K=4096 N=4096 M=16 call"},
