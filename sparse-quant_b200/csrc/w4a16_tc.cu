@@ -394,8 +394,10 @@ int g_force_tok = 0, g_force_split = 0;
 
 struct TcPlan { int tok, split; };
 
-// Token tile and K split by a cost model in SM clocks: waves of work items x (k-steps x max(MMA, dequant) +
-// epilogue) plus, for split-K, the round trip of the fp32 partial tiles through L2.
+// Token tile and K split by a cost model in SM clocks, fitted to measurements on B200: a work item costs
+// (k-steps x max(MMA, dequant) + epilogue), where the dequantisers need about 800 + 0.6 x tokens clocks per 64-k
+// step whatever the token tile (the MMA only 2 x tokens), items run in waves of one per SM, and split-K adds the
+// round trip of the fp32 partial tiles through L2/HBM at about 650 bytes per clock.
 TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0)
 {
     const int n_blocks = (N + kBlockN - 1) / kBlockN;
@@ -409,14 +411,14 @@ TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0
         for (int sp = 1; sp <= 4; sp *= 2) {
             if (g_force_split && !force_split ? sp != g_force_split : (sp > 1 && !allow_split)) continue;
             if (sp > 1 && k_steps / sp < 8) continue;
-            // measured: splitting only pays when K is long and the unsplit tiles leave most SMs idle
-            if (sp > 1 && !g_force_split && !force_split && (K < 8192 || sp != 2 || (long long)n_blocks * ((tokens + t - 1) / t) * 2 > 148)) continue;
+            if (sp > 1 && K < 8192 && !g_force_split && !force_split) continue;      // measured: no gain from splitting a short K
             if (force_split && sp != force_split) continue;
             const long long items = (long long)n_blocks * ((tokens + t - 1) / t) * sp;
             const long long waves = (items + 147) / 148;
-            const double step = 2.0 * t > 240 ? 2.0 * t : 240;                       // MMA vs dequant bound
+            const double dequant = 800.0 + 0.6 * t;
+            const double step = 2.0 * t > dequant ? 2.0 * t : dequant;
             double cost = waves * ((double)(k_steps / sp) * step + 6.0 * t + 2000);
-            if (sp > 1) cost += (double)sp * tokens * N * 8.0 / 3000.0 + 3000;       // partials written + read back (~3 KB/clk)
+            if (sp > 1) cost += (double)sp * tokens * N * 8.0 / 650.0 + 3000;        // partials written + read back
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {t, sp}; }
         }
     }
