@@ -8,12 +8,12 @@
 // out-features per CTA tile), the activations are "B" (N = 64/128/256 tokens), the fp32
 // accumulator D[out-feature lane][token column] lives in tensor memory.
 //
-// One persistent CTA per SM, 192 threads, warp specialised:
+// One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6.. dequantisers, 4 TMA, 5 MMA):
 //   warp 4   TMA producer: per 64-k step one tensor copy of the activation tile (128-byte
 //            swizzle, K-major) plus plain bulk copies of the packed weight tiles (a k-tile row
 //            of the format is contiguous) and of the group's (zero, scale) row; all complete on
 //            one mbarrier per stage.  No cluster fan-out is used anywhere.
-//   warps0-3 dequantisers: read 16 B per lane per 32x32 tile from shared memory, expand the
+//   warps0-3,6.. dequantisers (groups of four taking k-steps in turn): read 16 B per lane per 32x32 tile from shared memory, expand the
 //            nibbles in registers, (t - z) * s with sub.ftz/mul.ftz (bit-exact with the
 //            reference), and write the fp16 result straight into tensor memory with
 //            tcgen05.st.16x128b - the packed layout is already that fragment order - so the
@@ -38,7 +38,13 @@ namespace {
 
 constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 packed tiles)
 constexpr int kBlockK   = 64;                  // k per stage (2 packed tiles)
-constexpr int kThreads  = 320;                 // warps 0-3, 6-9: dequantisers; warp 4: TMA; warp 5: MMA
+// Measured on B200 (M = 8192): 2 groups 1136 / 1148 / 1256 TFLOP/s, 4 groups 1104 / 1111 / 1206 - the dequantisers are
+// not the limit once two steps are in flight (under the power cap the SM clock, not the issue rate, sets the pace).
+#ifndef W4A16_TC_DEQUANT_GROUPS
+#define W4A16_TC_DEQUANT_GROUPS 2
+#endif
+constexpr int kDequantGroups = W4A16_TC_DEQUANT_GROUPS;    // groups of four dequantiser warps taking k-steps in turn
+constexpr int kThreads  = 64 + 128 * kDequantGroups;       // warps 0-3, 6-9, 10-13, ...: dequantisers; warp 4: TMA; warp 5: MMA
 constexpr int kTmemCols = 512;
 #ifndef W4A16_TC_STAGES_256
 #define W4A16_TC_STAGES_256 6
@@ -190,16 +196,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             }
         }
     } else {
-        // ------------------------------ dequant + epilogue (warps 0..3 and 6..9) ------------------------------
-        // Two groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which is
-        // also the packed tile column it dequantises.  Group 0 takes the even k-steps, group 1 the odd ones
-        // (counted across tiles, so the alternation follows the stage ring); each group drains half of the
-        // accumulator columns in the epilogue.
+        // ------------------------------ dequant + epilogue (warps 0..3 and 6..) ------------------------------
+        // kDequantGroups groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which
+        // is also the packed tile column it dequantises.  Group g takes the k-steps with (step % groups) == g
+        // (counted across tiles, so the rotation follows the stage ring): one step keeps a warp busy for a chain of
+        // dependent latencies (shared-memory load, unpack, sub/mul, tcgen05.st, its completion), so the dequant
+        // rate is set by how many steps are in flight, not by issue slots.  Groups 0 and 1 also drain the
+        // accumulator (half of the columns each) in the epilogue; the others run ahead into the next tile.
         int stage = 0; uint32_t phase = 0, dphase = 0;
         bool ok = true;
         const int r = lane >> 2;
-        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : 1;
-        uint32_t step_parity = 0, epi_phase = 0;
+        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : (warp - 2) / 4;
+        uint32_t step_mod = 0, epi_phase = 0;
         // bounded rendezvous of the eight dequant/epilogue warps (split-K finalisation)
         auto epi_sync = [&]() -> bool {
             __syncwarp();
@@ -215,8 +223,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             const bool has_tile = nb * 4 + quarter < n_tiles;
             int ks0, ks1;
             k_range(item, ks0, ks1);
-            for (int ks = ks0; ks < ks1; ++ks, step_parity ^= 1u) {
-                if (step_parity != (uint32_t)dgroup) {                 // the other group's stage
+            for (int ks = ks0; ks < ks1; ++ks, step_mod = (step_mod + 1 == (uint32_t)kDequantGroups ? 0u : step_mod + 1)) {
+                if (step_mod != (uint32_t)dgroup) {                    // another group's stage
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                     continue;
                 }
@@ -256,6 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 if (++stage == S) { stage = 0; phase ^= 1u; }
             }
             if (!ok) break;
+            if (dgroup >= 2) continue;                                   // only groups 0 and 1 drain the accumulator
 
             // epilogue: thread = out-feature (TMEM lane), registers = tokens
             ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, dphase, abort_flag, kWaitBudgetNs));
@@ -394,10 +403,10 @@ int g_force_tok = 0, g_force_split = 0;
 
 struct TcPlan { int tok, split; };
 
-// Token tile and K split by a cost model in SM clocks, fitted to measurements on B200: a work item costs
-// (k-steps x max(MMA, dequant) + epilogue), where the dequantisers need about 800 + 0.6 x tokens clocks per 64-k
-// step whatever the token tile (the MMA only 2 x tokens), items run in waves of one per SM, and split-K adds the
-// round trip of the fp32 partial tiles through L2/HBM at about 650 bytes per clock.
+// Token tile and K split by a cost model in SM clocks (at the nominal clock), fitted to measurements on B200: a work
+// item costs k-steps x step + epilogue, where a 64-k step was measured at about 800 + 0.6 x tokens clocks whatever the
+// token tile (the MMA alone would need 2 x tokens), items run in waves of one per SM, and split-K adds the round trip
+// of the fp32 partial tiles through L2/HBM at about 650 bytes per clock.
 TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0)
 {
     const int n_blocks = (N + kBlockN - 1) / kBlockN;
@@ -415,8 +424,8 @@ TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0
             if (force_split && sp != force_split) continue;
             const long long items = (long long)n_blocks * ((tokens + t - 1) / t) * sp;
             const long long waves = (items + 147) / 148;
-            const double dequant = 800.0 + 0.6 * t;
-            const double step = 2.0 * t > dequant ? 2.0 * t : dequant;
+            const double measured = 800.0 + 0.6 * t;
+            const double step = 2.0 * t > measured ? 2.0 * t : measured;
             double cost = waves * ((double)(k_steps / sp) * step + 6.0 * t + 2000);
             if (sp > 1) cost += (double)sp * tokens * N * 8.0 / 650.0 + 3000;        // partials written + read back
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {t, sp}; }
