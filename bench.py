@@ -604,9 +604,10 @@ def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
             od[(M, K, N)] = torch.empty(M, nl, dtype=torch.float16, device=dev)
     calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
 
-    side = torch.cuda.Stream(device=dev)
-    lanes = [sp, side.cuda_stream]
-    lane_of = {key: i % 2 for i, key in enumerate(xh)}       # calls sharing staging buffers stay on one stream
+    n_lanes = int(os.environ.get("W4A16_E2E_STREAMS", "4"))
+    sides = [torch.cuda.Stream(device=dev) for _ in range(max(1, n_lanes) - 1)]
+    lanes = [sp] + [s_.cuda_stream for s_ in sides]
+    lane_of = {key: i % len(lanes) for i, key in enumerate(xh)}       # calls sharing staging buffers stay on one stream
 
     def one(c, fn, st=None):
         M, K, N, s = c
@@ -646,11 +647,12 @@ def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
         for c in calls:
             one(c, lib.w4a16_gemm_host_async, lanes[lane_of[c[:3]]])
         stream.synchronize()
-        side.synchronize()
+        for s_ in sides:
+            s_.synchronize()
     wall = time.perf_counter() - t0
     return {"value": step_bytes * steps / wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "steps": steps, "ms_per_step": 1e3 * wall / steps,
-            "timer": "host wall clock; per step: all calls enqueued through w4a16_gemm_host_async (pinned host x in, y out) on two streams, one synchronisation",
+            "timer": f"host wall clock; per step: all calls enqueued through w4a16_gemm_host_async (pinned host x in, y out) on {len(lanes)} streams, one synchronisation",
             "per_call_sync": {"value": step_bytes * steps / wall_sync / 1e9, "ms_per_step": 1e3 * wall_sync / steps,
                               "device_event_ms_per_step": dev_ms,
                               "what": "w4a16_gemm_host: every call synchronises before it returns"}}
