@@ -319,15 +319,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     if (stage_x) mbar_wait(xbar, 0, abort_flag, kWaitBudgetNs);
     if (tl) tl[1] = globaltimer_ns();
 
-    // sum_k x[t, k] per quantisation group of this CTA's K range, once per CTA: an MMA with an all-ones A
-    // fragment over the staged activations (every row of the result holds the sums), groups dealt round-robin
-    // to the warps; the main loop reads them back when it applies the zero points.
+    // sum_k x[t, k] per quantisation group, by an MMA with an all-ones A fragment over the staged activations (every
+    // row of the result holds the sums); the main loop reads them back when it applies the zero points.  With one
+    // out-feature tile per CTA every warp owns a different K slice and computes just its own groups - nobody else
+    // needs them, so a warp-level barrier is enough.  With several tiles per CTA the warps of a K slice would repeat
+    // each other's work: the groups of the whole CTA are dealt round-robin and a CTA-wide barrier follows.
     {
         float* xsum_w = reinterpret_cast<float*>(smem + p.xsum_offset);
-        const int cta_groups = (min(cu1 * kUnitK, p.K) - cu0 * kUnitK) / G;
+        const int k_end = min(cu1 * kUnitK, p.K);
+        const int cta_groups = (k_end - cu0 * kUnitK) / G;
+        const bool own_slice = wn == 1;
+        const int g_lo = own_slice ? (wu0 - cu0) * (kUnitK / G) : warp;
+        const int g_hi = own_slice ? (min(wu1 * kUnitK, p.K) - cu0 * kUnitK) / G : cta_groups;
+        const int g_step = own_slice ? 1 : kWarps;
         constexpr uint32_t kOnes = 0x3c003c00u;
         const uint32_t ones[4] = {kOnes, kOnes, kOnes, kOnes};
-        for (int gidx = warp; gidx < cta_groups; gidx += kWarps) {
+        for (int gidx = g_lo; gidx < g_hi; gidx += g_step) {
 #pragma unroll
             for (int tg = 0; tg < TG; ++tg) {
                 const int row = tg * 8 + (lane & 7);
@@ -344,8 +351,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                 if (lane < 4) *reinterpret_cast<float2*>(xsum_w + gidx * kTok + tg * 8 + 2 * lane) = make_float2(sum[0], sum[1]);
             }
         }
+        if (own_slice) __syncwarp();
+        else __syncthreads();
     }
-    __syncthreads();
     if (tl) tl[2] = globaltimer_ns();
 
     float acc[TG][2][4];
