@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         return;
     }
     const int cur = (int)cur_ll, n = cur + 1;
-    const int t_lo = (int)((long long)n * rank / S), t_hi = (int)((long long)n * (rank + 1) / S);   // the last rank owns `cur`
+    const int t_lo = (int)((unsigned)(n * rank) / (unsigned)S), t_hi = (int)((unsigned)(n * (rank + 1)) / (unsigned)S);   // the last rank owns `cur`
     const size_t row0 = ((size_t)b * p.heads + head) * p.max_len;          // first cache row of this (sequence, head)
     const __half* qrow = p.qkv + (size_t)b * p.qkv_stride + head * D;
     const __half* krow = qrow + p.heads * D;

@@ -74,6 +74,8 @@ struct SkinnyParams {
     int*            error;
     int tokens, N, K;
     int wn;          // out-feature tiles per CTA (1,2,4,8,16); WK = 16 / wn K-slices per CTA
+    int wn_shift;    // log2(wn)
+    unsigned inv_splits;   // ceil(2^32 / splits): x / splits == umulhi(x, inv_splits) for the small x used here
     int splits;      // cluster size along K (gridDim.y)
     int xs_stride;   // halfs per staged activation row
     int xsum_offset; // byte offset of the per-group activation sums [groups of the CTA][tokens] fp32
@@ -229,8 +231,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     static_assert(sizeof(SlotT) % 16 == 0, "bulk copies need 16-byte aligned destinations");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wn = p.wn, wk = kWarps / wn;
-    const int wn_idx = warp % wn, wk_idx = warp / wn;
+    // all index arithmetic below is shifts, masks and one multiply-high: a 64-bit division costs about a hundred
+    // instructions per thread, and with ~30 tiles per warp the fixed part of the kernel is what the small shapes pay for
+    static_assert((kWarps & (kWarps - 1)) == 0, "power-of-two warp count");
+    const int wn = p.wn, wk = kWarps >> p.wn_shift;
+    const int wn_idx = warp & (wn - 1), wk_idx = warp >> p.wn_shift;
+    const int wk_sh = 31 - __clz(wk);
     const int n_tiles = p.N / kTileN;
     const int nt = blockIdx.x * wn + wn_idx;
     const bool nt_valid = nt < n_tiles;
@@ -241,9 +247,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     const int k_tiles = p.K / kTileK;
     const int units = (p.K + kUnitK - 1) / kUnitK;
     const int S = p.splits, rank = blockIdx.y;
-    const int cu0 = (int)((long long)units * rank / S), cu1 = (int)((long long)units * (rank + 1) / S);
+    auto div_splits = [&](int x) { return S == 1 ? x : (int)__umulhi((unsigned)x, p.inv_splits); };
+    const int cu0 = div_splits(units * rank), cu1 = div_splits(units * (rank + 1));
     const int cta_units = cu1 - cu0;
-    const int wu0 = cu0 + (int)((long long)cta_units * wk_idx / wk), wu1 = cu0 + (int)((long long)cta_units * (wk_idx + 1) / wk);
+    const int wu0 = cu0 + ((cta_units * wk_idx) >> wk_sh), wu1 = cu0 + ((cta_units * (wk_idx + 1)) >> wk_sh);
     const int n_units = nt_valid ? wu1 - wu0 : 0;
 
     // shared memory: header (kHeaderBytes): [16 B zeros][abort flag][barriers kMaxWarps x kDepth] | activations | per-warp rings
@@ -443,7 +450,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     // the sum of S * wk partials - K slice w of rank q lives in the ring of warp (w * wn + n_local / 32) -
     // added in a fixed order (rank-major) from batches of eight loads in flight: deterministic.
     const int Er = rows << nloc_shift, terms = S << wk_shift;
-    const int e_lo = (int)((long long)Er * rank / S), e_hi = (int)((long long)Er * (rank + 1) / S);
+    const int e_lo = div_splits(Er * rank), e_hi = div_splits(Er * (rank + 1));
     for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
         const int tok = e >> nloc_shift, nl = e & (nloc - 1);
         const int off = (nl >> 5) * kRingFloats + tok * 33 + (nl & 31);
@@ -757,6 +764,9 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
         }
         p.world = x.world; p.rank = x.rank; p.capacity = x.capacity; p.self = x.peer[x.rank];
     }
+    p.wn_shift = 0;
+    while ((1 << p.wn_shift) < c.wn) ++p.wn_shift;
+    p.inv_splits = c.splits > 1 ? (unsigned)(((1ull << 32) + c.splits - 1) / c.splits) : 0u;
     p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0; p.relu = a.relu ? 1 : 0;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
