@@ -13,8 +13,9 @@ SwiGLU, no biases, untied fp16 lm_head).
 
 Tensor parallelism (one process per GPU): q/k/v and fc1 (gate/up) column-parallel with attention
 heads split across ranks, out_proj and fc2 (down) row-parallel with one all-reduce each, lm_head
-split by vocabulary with an all-gather of the logits.  Weights are synthetic: every rank generates
-the full packed tensors of a layer from the same seed and keeps its exact shard.
+split by vocabulary with an all-gather of the logits.  Parameters come from a "source": synthetic by
+default (every rank generates the full packed tensors of a layer from the same seed and keeps its exact
+shard), or the state dict of a model quantised and saved by the reference (w4a16/checkpoint.py).
 """
 from __future__ import annotations
 
@@ -67,6 +68,31 @@ def synthetic_walinear(in_features, out_features, group_size, bias, seed, device
     return lin
 
 
+class SyntheticSource:
+    """Where a Decoder gets its parameters from.  This one makes them up (random init, deterministic in `seed`): every
+    rank generates the full tensors of a layer from the same seed and keeps its exact shard.  checkpoint.StateDictSource
+    serves the tensors of a model quantised and saved by the reference instead."""
+
+    def __init__(self, cfg: "DecoderConfig", seed: int, device):
+        self.cfg, self.seed, self.device = cfg, seed, device
+        self.gen = torch.Generator(device=device).manual_seed(seed)
+        self._slots = {"q_proj": 0, "k_proj": 1, "v_proj": 2, "out_proj": 3, "fc1": 4, "gate_proj": 4, "up_proj": 5,
+                       "fc2": 6, "down_proj": 6}
+
+    def linear(self, layer: int, name: str, in_features: int, out_features: int) -> WALinear:
+        """The full (unsharded) packed linear `name` of decoder layer `layer`."""
+        return synthetic_walinear(in_features, out_features, self.cfg.group_size, self.cfg.kind == "opt",
+                                  self.seed + 100 * layer + self._slots[name], self.device)
+
+    def norm(self, layer, name: str, module: nn.Module) -> nn.Module:
+        """Fill the normalisation `name` ("ln1", "ln2" of a layer, or "final" with layer None); default init here."""
+        return module
+
+    def table(self, name: str, rows: int, cols: int) -> torch.Tensor:
+        """fp16 [rows, cols]: "embed", "pos_embed" (OPT) or "lm_head" (LLaMA; OPT ties it to "embed")."""
+        return (torch.randn((rows, cols), device=self.device, generator=self.gen) * 0.02).to(torch.float16)
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim, eps, device):
         super().__init__()
@@ -80,33 +106,33 @@ class RMSNorm(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, group, device, seed: int, exchange=None):
+    def __init__(self, cfg: DecoderConfig, idx: int, rank: int, world: int, group, device, source, exchange=None):
         super().__init__()
         self.cfg, self.rank, self.world = cfg, rank, world
         H, g = cfg.hidden, cfg.group_size
-        bias = cfg.kind == "opt"
         self.head_dim = H // cfg.heads
         assert cfg.heads % world == 0, "attention heads must divide evenly over the ranks"
         self.local_heads = cfg.heads // world
         head_ranges = [(r * self.local_heads * self.head_dim, (r + 1) * self.local_heads * self.head_dim) for r in range(world)]
         ffn_ranges = shard_ranges(cfg.ffn, math.lcm(32, g), world)        # shared by fc1/gate/up (columns) and fc2/down (rows)
-        s = seed + 100 * idx
 
-        def col(i, n_out, ranges):
-            return ColumnParallelWALinear(synthetic_walinear(H, n_out, g, bias, s + i, device), rank, world, ranges=ranges)
+        def col(name, n_out, ranges):
+            return ColumnParallelWALinear(source.linear(idx, name, H, n_out), rank, world, ranges=ranges)
 
         # q/k/v (and gate/up below) are sharded one by one, then this rank's shards are fused in the packed domain
         # into one linear: one GEMV launch instead of three, and the layout the decode attention kernel reads
-        self.qkv_proj = fuse_columns([col(0, H, head_ranges), col(1, H, head_ranges), col(2, H, head_ranges)])
-        self.out_proj = RowParallelWALinear(synthetic_walinear(H, H, g, bias, s + 3, device), rank, world, group, ranges=head_ranges, exchange=exchange)
+        self.qkv_proj = fuse_columns([col("q_proj", H, head_ranges), col("k_proj", H, head_ranges), col("v_proj", H, head_ranges)])
+        self.out_proj = RowParallelWALinear(source.linear(idx, "out_proj", H, H), rank, world, group, ranges=head_ranges, exchange=exchange)
         if cfg.kind == "opt":
-            self.fc1 = col(4, cfg.ffn, ffn_ranges)
-            self.ln1 = nn.LayerNorm(H, device=device, dtype=torch.float16)
-            self.ln2 = nn.LayerNorm(H, device=device, dtype=torch.float16)
+            self.fc1 = col("fc1", cfg.ffn, ffn_ranges)
+            self.ln1 = source.norm(idx, "ln1", nn.LayerNorm(H, device=device, dtype=torch.float16))
+            self.ln2 = source.norm(idx, "ln2", nn.LayerNorm(H, device=device, dtype=torch.float16))
+            self.fc2 = RowParallelWALinear(source.linear(idx, "fc2", cfg.ffn, H), rank, world, group, ranges=ffn_ranges, exchange=exchange)
         else:
-            self.gate_up_proj = fuse_columns([col(4, cfg.ffn, ffn_ranges), col(5, cfg.ffn, ffn_ranges)])
-            self.ln1, self.ln2 = RMSNorm(H, cfg.rms_eps, device), RMSNorm(H, cfg.rms_eps, device)
-        self.fc2 = RowParallelWALinear(synthetic_walinear(cfg.ffn, H, g, bias, s + 6, device), rank, world, group, ranges=ffn_ranges, exchange=exchange)
+            self.gate_up_proj = fuse_columns([col("gate_proj", cfg.ffn, ffn_ranges), col("up_proj", cfg.ffn, ffn_ranges)])
+            self.ln1 = source.norm(idx, "ln1", RMSNorm(H, cfg.rms_eps, device))
+            self.ln2 = source.norm(idx, "ln2", RMSNorm(H, cfg.rms_eps, device))
+            self.fc2 = RowParallelWALinear(source.linear(idx, "down_proj", cfg.ffn, H), rank, world, group, ranges=ffn_ranges, exchange=exchange)
         self.k_cache = self.v_cache = None
 
     def alloc_cache(self, batch, max_len, device):
@@ -178,21 +204,22 @@ def apply_rope(x, cos, sin):
 
 class Decoder(nn.Module):
     def __init__(self, cfg: DecoderConfig, rank: int = 0, world: int = 1, group=None, device="cuda", seed: int = 1234,
-                 exchange=None):
+                 exchange=None, source=None):
         """exchange: a tp.PeerExchange (capacity >= 32 * hidden).  With it the one-token step contains no library
         collective: row-parallel sums are done inside the decode kernel and the ranks' best logits are gathered
         through the same buffers, so the step can be captured in a CUDA graph at any world size."""
         super().__init__()
         self.cfg, self.rank, self.world, self.group, self.device = cfg, rank, world, group, torch.device(device)
         self.exchange = exchange
-        gen = torch.Generator(device=device).manual_seed(seed)
+        if source is None:
+            source = SyntheticSource(cfg, seed, device)      # `source`: where the parameters come from (see SyntheticSource)
         H = cfg.hidden
-        self.embed = (torch.randn((cfg.vocab, H), device=device, generator=gen) * 0.02).to(torch.float16)
+        self.embed = source.table("embed", cfg.vocab, H)
         if cfg.kind == "opt":
-            self.pos_embed = (torch.randn((cfg.max_positions + 2, H), device=device, generator=gen) * 0.02).to(torch.float16)
-            self.final_norm = nn.LayerNorm(H, device=device, dtype=torch.float16)
+            self.pos_embed = source.table("pos_embed", cfg.max_positions + 2, H)
+            self.final_norm = source.norm(None, "final", nn.LayerNorm(H, device=device, dtype=torch.float16))
         else:
-            self.final_norm = RMSNorm(H, cfg.rms_eps, device)
+            self.final_norm = source.norm(None, "final", RMSNorm(H, cfg.rms_eps, device))
             inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, H // cfg.heads, 2, device=device).float() / (H // cfg.heads)))
             t = torch.arange(cfg.max_positions, device=device).float()
             emb = torch.cat((torch.outer(t, inv),) * 2, dim=-1)
@@ -201,9 +228,9 @@ class Decoder(nn.Module):
         self.vocab_ranges = shard_ranges(cfg.vocab, 1, world) if cfg.vocab % world else \
             [(r * cfg.vocab // world, (r + 1) * cfg.vocab // world) for r in range(world)]
         v0, v1 = self.vocab_ranges[rank]
-        head_full = self.embed if cfg.kind == "opt" else (torch.randn((cfg.vocab, H), device=device, generator=gen) * 0.02).to(torch.float16)
+        head_full = self.embed if cfg.kind == "opt" else source.table("lm_head", cfg.vocab, H)
         self.lm_head = head_full[v0:v1].contiguous()
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, rank, world, group, device, seed, exchange) for i in range(cfg.layers))
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, rank, world, group, device, source, exchange) for i in range(cfg.layers))
         self.pos = 0
 
     def mark_static(self):
