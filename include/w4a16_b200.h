@@ -248,8 +248,9 @@ int w4a16_static_scratch_error_flag(int* flag);
 /*
  * Both GEMM kernels bound every barrier wait; if one ever times out the kernel sets a
  * per-device error word, releases what it holds (tensor memory) and returns.  This reads that
- * word (*flag = 0: no kernel on the current device ever gave up).  Synchronises the device; the
- * first call on a device allocates the word, so make it outside stream capture.  The
+ * word (*flag = 0: no kernel on the current device ever gave up; 1: a barrier wait inside a GEMM kernel timed out;
+ * 2: a wait for a peer in the exchange gave up; 3: w4a16_decode_attention was given a position outside the
+ * cache).  Synchronises the device; the first call on a device allocates the word, so make it outside stream capture.  The
  * reference has no counterpart (it checks no CUDA error at all, gemm_s4_f16_kernel.h:136-145).
  */
 int w4a16_device_error_flag(int* flag);
