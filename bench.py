@@ -1,23 +1,30 @@
 #!/usr/bin/env python3
 """Benchmark of the W4A16 hot path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-prefill] [--no-cpu]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-prefill] [--no-cpu] [--no-models]
 
 Headline (`value`): the OPT-6.7B-shaped decode sweep - M in {1,4,8,16} on (K,N) in
 {(4096,4096), (4096,16384), (16384,4096)}, g=128 - as achieved HBM GB/s (algorithmic bytes /
-device time), inputs resident in HBM.  One step = the 12 (shape, M) launches, each run once on
-every one of SETS distinct weight sets (rotating, so the bytes touched between two uses of a set
-exceed the 126 MB L2).  The step is captured in a CUDA graph; K graph replays are timed with CUDA
-events on the launching stream.  Extra keys: `e2e` (same sweep through the host-buffer C-ABI call),
-`roofline`, `cpu_baseline`, `prefill` (tcgen05 GEMM TFLOP/s, M in {512,2048,8192}), `sweep`
-(per-shape decode numbers), `clocks`.
+device time), inputs resident in HBM.  One step = ROUNDS passes over the 12 (shape, M) launches;
+every launch of a step reads its own weight set, so no packed byte is read twice within a step and
+the bytes that pass between two uses of a set (one whole step) are several times the L2 size.  The
+step is captured in a CUDA graph; K replays are timed with CUDA events on the launching stream.
+Extra keys: `e2e` (same sweep through the host-buffer C-ABI call), `roofline`, `cpu_baseline`,
+`sweep` (per-shape decode numbers, min and median), `prefill` (tcgen05 GEMM TFLOP/s, M in
+{512,2048,8192}), `ref_kernel` (the reference's own CUDA kernel rebuilt for sm_100a, timed on the
+same box where its rows are self-consistent), `model_opt67b` / `model_llama2_7b` (full decoder
+stacks: prefill and decode tokens/s at this number of GPUs), `tp_check` (N > 1: the fused
+row-parallel sum against the NCCL route and across ranks), `clocks`.
 
 `--impl reference` times the CPU restatement of the reference path (dequantise + fp32 matmul) on
 the host cores instead; the reference ships no CPU implementation of its own.
 """
 import argparse
 import ctypes
+import glob
+import importlib.util
 import json
+import math
 import os
 import sys
 import threading
@@ -38,8 +45,12 @@ G = 128
 DECODE_SHAPES = [(4096, 4096), (4096, 16384), (16384, 4096)]     # (K, N)
 DECODE_M = [1, 4, 8, 16]
 PREFILL_M = [512, 2048, 8192]
-SETS = 4                                                         # distinct weight sets per shape
+ROUNDS = 32                                                      # passes over the 12 (shape, M) launches per step
 WORKLOAD = "OPT-6.7B decode GEMV sweep: M in {1,4,8,16} x (K,N) in {4096x4096, 4096x16384, 16384x4096}, g=128"
+# DRAM bytes moved per algorithmic byte, from an ncu capture of 12 consecutive launches of the step
+# (profiles/gemv_kernel_step_order_dram_bytes.md: dram__bytes_read.sum + dram__bytes_write.sum over the launches
+# divided by their algorithmic bytes)
+TRAFFIC_RATIO = 1.0004
 
 
 def decode_bytes(M, K, N, g=G, bias=False):
@@ -136,62 +147,87 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # reference / CPU arm
 # ---------------------------------------------------------------------------------------------
-def cpu_pass(K, N, M, qw_np, zs_np, x):
+def cpu_pass(K, N, qw_np, zs_np, x):
     import oracle
     w = oracle.dequant_f32(qw_np, zs_np, K, N, G)                 # C + OpenMP, bit-exact dequantisation
     return torch.matmul(x.float(), torch.from_numpy(w).t())       # fp32 matmul on all host threads
 
 
-class CpuCase:
-    """One bounded sample of the workload for the host cores: the K=4096 N=4096 M=16 call."""
-    K, N, M = 4096, 4096, 16
+class CpuSweep:
+    """The decode sweep on the host cores: per (shape, M) one dequantise (C/OpenMP, all threads) + torch fp32 matmul,
+    as the reference's CPU-runnable check does it (dequantise, then matmul)."""
 
     def __init__(self):
         import oracle
         torch.set_num_threads(os.cpu_count() or 1)
         rng = np.random.default_rng(0)
-        self.qw = rng.integers(0, 2 ** 32, size=(self.K, self.N // 8), dtype=np.uint32)
-        zs = np.empty((self.K // G, 2 * self.N), dtype=np.float16)
-        zs[:, 0::2] = rng.integers(5, 11, size=(self.K // G, self.N)) + 64
-        zs[:, 1::2] = rng.random((self.K // G, self.N)) * 0.004 + 0.006
-        self.zs = zs.view(np.uint16)
-        self.x = torch.randn(self.M, self.K).half()
+        self.w = {}
+        for (K, N) in DECODE_SHAPES:
+            qw = rng.integers(0, 2 ** 32, size=(K, N // 8), dtype=np.uint32)
+            zs = np.empty((K // G, 2 * N), dtype=np.float16)
+            zs[:, 0::2] = rng.integers(5, 11, size=(K // G, N)) + 64
+            zs[:, 1::2] = rng.random((K // G, N)) * 0.004 + 0.006
+            self.w[(K, N)] = (qw, zs.view(np.uint16))
+        self.x = {(M, K): torch.randn(M, K).half() for (K, _) in DECODE_SHAPES for M in DECODE_M}
         self.cores = max(oracle.num_threads(), torch.get_num_threads())
-        self.bytes = decode_bytes(self.M, self.K, self.N)
-        self.run()                                                # warm (library load, thread pools)
+        self.calls = [(M, K, N) for (K, N) in DECODE_SHAPES for M in DECODE_M]
+        self.call(16, 4096, 4096)                                  # warm (library load, thread pools)
 
-    def run(self):
+    def call(self, M, K, N):
         t0 = time.perf_counter()
-        cpu_pass(self.K, self.N, self.M, self.qw, self.zs, self.x)
+        cpu_pass(K, N, *self.w[(K, N)], self.x[(M, K)])
         return time.perf_counter() - t0
 
+    def run(self, calls):
+        return sum(self.call(*c) for c in calls)
 
-def cpu_baseline(repeat=3):
-    case = CpuCase()
-    dt = float(np.mean([case.run() for _ in range(repeat)]))
-    return dict(value=case.bytes / dt / 1e9, unit=UNIT, cores=case.cores, kind="port",
-                sample=f"{repeat} pass(es) of the K=4096 N=4096 M=16 call (dequantise in C/OpenMP + torch fp32 matmul)",
-                seconds_per_pass=dt)
+    def pick_sample(self, steps, budget_s=150.0):
+        """The largest sample of the sweep that lets `steps` steps finish within the budget: the 12 calls, the three
+        M=16 calls, or the single K=4096 N=4096 M=16 call."""
+        per_call = {c: self.call(*c) for c in [(16, K, N) for (K, N) in DECODE_SHAPES]}
+        est12 = 4.0 * sum(per_call.values())
+        if est12 * steps <= budget_s:
+            return self.calls, "the 12 (shape, M) calls of the sweep, once"
+        if sum(per_call.values()) * steps <= budget_s:
+            return [(16, K, N) for (K, N) in DECODE_SHAPES], "the three M=16 calls of the sweep, once"
+        return [(16, 4096, 4096)], "one K=4096 N=4096 M=16 call"
+
+
+def cpu_baseline():
+    sweep = CpuSweep()
+    rows = []
+    total_t, total_b = 0.0, 0
+    for (M, K, N) in sweep.calls:
+        dt = sweep.call(M, K, N)
+        b = decode_bytes(M, K, N)
+        rows.append({"K": K, "N": N, "M": M, "seconds": dt, "GBps": b / dt / 1e9})
+        total_t += dt
+        total_b += b
+    return dict(value=total_b / total_t / 1e9, unit=UNIT, cores=sweep.cores, kind="port",
+                sample="one pass of the 12 (shape, M) calls of the sweep (dequantise in C/OpenMP + torch fp32 matmul, all host threads)",
+                seconds_per_pass=total_t, rows=rows)
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    case = CpuCase()
+    sweep = CpuSweep()
+    calls, what = sweep.pick_sample(args.steps + args.warmup)
     for _ in range(args.warmup):
-        case.run()
-    times = [case.run() for _ in range(args.steps)]
+        sweep.run(calls)
+    times = [sweep.run(calls) for _ in range(args.steps)]
     dt = float(np.sum(times))
-    v = case.bytes * args.steps / dt / 1e9
-    cb = dict(value=v, unit=UNIT, cores=case.cores, kind="port",
-              sample=f"{args.steps} step(s), each one pass of the K=4096 N=4096 M=16 call (dequantise in C/OpenMP + torch fp32 matmul)")
+    nbytes = sum(decode_bytes(*c) for c in calls)
+    v = nbytes * args.steps / dt / 1e9
+    cb = dict(value=v, unit=UNIT, cores=sweep.cores, kind="port",
+              sample=f"{args.steps} step(s), each {what} (dequantise in C/OpenMP + torch fp32 matmul, all host threads)")
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16xs4->f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference path (the reference ships no CPU code for it); "
-                                                 "each step is a bounded sample: one K=4096 N=4096 M=16 call"},
+                                                 f"each step is a bounded sample of the sweep: {what}"},
         "cpu_baseline": cb,
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -224,14 +260,17 @@ def make_exchange(capacity, dev, dist):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rounds", type=int, default=ROUNDS, help="passes over the 12 (shape, M) launches per step")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--small", action="store_true", help="one weight set, no extras (for profiler captures)")
+    ap.add_argument("--no-models", action="store_true", help="skip the decoder-stack numbers after the sweep")
+    ap.add_argument("--no-ref-kernel", action="store_true", help="skip timing the rebuilt reference kernel")
+    ap.add_argument("--small", action="store_true", help="the timed sweep only, no extras (for profiler captures)")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
-                    help="capture the step in a CUDA graph (auto: on unless NCCL collectives are in the step)")
+                    help="capture the step in a CUDA graph (never when NCCL collectives are in the step)")
     ap.add_argument("--reduce", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how row-parallel outputs are summed - inside the decode kernel through peer memory, or by an NCCL all-reduce")
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
@@ -239,8 +278,8 @@ def main():
                     help="decode-sweep (default, the headline metric) or a full random-init W4A16 decoder stack: prefill + greedy decode tokens/s")
     ap.add_argument("--layers", type=int, default=0, help="override the number of decoder layers of a model workload")
     ap.add_argument("--single", default=None, metavar="K,N,M[,ALGO[,REPS]]",
-                    help="only launch one shape REPS times over 4 rotating weight sets and exit (driver for ncu captures); "
-                         "ALGO 0 auto, 1 skinny, 2 tcgen05")
+                    help="only launch one shape REPS times over rotating weight sets and exit (driver for ncu captures); "
+                         "ALGO 0 auto, 1 decode kernel, 2 tcgen05")
     ap.add_argument("--single-attention", default=None, metavar="B,H,D,L,POS[,REPS]",
                     help="only launch the decode attention kernel REPS times over 4 rotating caches and exit (driver for ncu captures)")
     args = ap.parse_args()
@@ -255,17 +294,10 @@ def main():
     if args.single_attention:
         run_single_attention(args.single_attention)
         return
-    if args.workload != "decode-sweep":
-        run_model(args)
-        return
 
     import quant
     lib = quant.load_library()
     rank = int(os.environ.get("RANK", "0"))
-
-    def note(msg):
-        if args.verbose:
-            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -274,12 +306,25 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-        note("process group up")
 
-    sets = 1 if args.small else SETS
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    if args.workload != "decode-sweep":
+        line = model_line(args, args.workload, rank, world, dev, dist)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        return
+
     peaks = measured_peaks()
     stream = torch.cuda.Stream(device=dev)
     sp = stream.cuda_stream
+    rounds = max(1, args.rounds)
+    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
 
     # Tensor-parallel sharding of the sweep at N > 1 (Megatron style, as the model builder does it):
     #   4096 x 4096  (q/k/v-type) and 4096 x 16384 (fc1): column-parallel, each rank owns N / world out-features;
@@ -298,10 +343,12 @@ def main():
         exchange = make_exchange(max(DECODE_M) * max(N for _, N in DECODE_SHAPES), dev, dist)
         note("peer exchange buffers mapped" if exchange is not None else "peer exchange unavailable: NCCL all-reduce instead")
 
+    # one weight set per launch of the step: rounds * len(DECODE_M) sets per shape
+    sets = rounds * len(DECODE_M)
     weights = {}
     for si, (K, N) in enumerate(DECODE_SHAPES):
         kl, nl, _ = local_shape(K, N)
-        weights[(K, N)] = [synth_packed(kl, nl, G, dev, 1234 + 10 * si + s + 100 * rank) for s in range(sets)]
+        weights[(K, N)] = [synth_packed(kl, nl, G, dev, 1234 + 1000 * si + s + 100000 * rank) for s in range(sets)]
     xs, outs = {}, {}
     for (K, N) in DECODE_SHAPES:
         kl, nl, _ = local_shape(K, N)
@@ -325,8 +372,10 @@ def main():
         if reduce and exchange is None:
             dist.all_reduce(outs[(M, K, N)])
 
-    calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
+    # order of a step: round by round, shape by shape, M by M - consecutive launches never share a weight set
+    calls = [(M, K, N, rd * len(DECODE_M) + mi) for rd in range(rounds) for (K, N) in DECODE_SHAPES for mi, M in enumerate(DECODE_M)]
     step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
+    distinct_weight_bytes = sum((K * N // 2 + (K // G) * N * 4) for (M, K, N, s) in calls) // world
     launches_per_step = len(calls)
     collectives_per_step = sum(1 for (M, K, N, s) in calls if local_shape(K, N)[2])
 
@@ -334,7 +383,7 @@ def main():
     if dist is not None:
         dist.barrier()                      # ranks enter the first exchange together
     with torch.cuda.stream(stream):
-        for c in calls:
+        for c in calls[:24]:
             launch(*c, sp)
     stream.synchronize()
     note("eager pass done")
@@ -345,7 +394,11 @@ def main():
             if err:
                 raise RuntimeError(f"peer exchange gave up waiting for rank {err - 1} ({where}, after {epoch} calls)")
     check_exchange("eager pass")
-    use_graph = args.graph == "on" or (args.graph == "auto" and (world == 1 or exchange is not None))
+    # NCCL collectives are never captured in a graph here: with the NCCL route the launches are stream-ordered
+    nccl_in_step = world > 1 and exchange is None
+    use_graph = args.graph != "off" and not nccl_in_step
+    if args.graph == "on" and nccl_in_step:
+        print("[bench] --graph on ignored: the step holds NCCL all-reduces, which are not captured", file=sys.stderr, flush=True)
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
@@ -373,20 +426,21 @@ def main():
     note("warm-up done")
     sampler = ClockSampler(local)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     t0 = time.perf_counter()
     with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(args.steps):
+        events[0].record(stream)
+        for i in range(args.steps):
             run_step()
-        e1.record(stream)
+            events[i + 1].record(stream)
     sampler.poll()
     barrier()
     check_exchange("timed region")
     note("timed region done")
     t1 = time.perf_counter()
     clocks = sampler.finish(t0, t1)
-    ms = e0.elapsed_time(e1)
+    ms = events[0].elapsed_time(events[-1])
+    step_ms = sorted(events[i].elapsed_time(events[i + 1]) for i in range(args.steps))
     if dist is not None:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -399,35 +453,56 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16xs4->f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "weight_sets": sets, "launches_per_step": launches_per_step,
-                   "l2": f"inputs larger than L2: {sets} rotating weight sets, {step_bytes / 1e6:.0f} MB touched per step",
+        "config": {"workload": WORKLOAD, "rounds_per_step": rounds, "launches_per_step": launches_per_step,
+                   "weight_sets_per_shape": sets,
+                   "l2": f"inputs larger than L2: every launch of a step reads its own weight set; {distinct_weight_bytes / 1e6:.0f} MB of "
+                         f"distinct packed bytes per GPU pass between two uses of a set (L2 = {l2_bytes / 1e6:.0f} MB)",
                    "timing": ("CUDA graph of one step, K replays between CUDA events on the launching stream" if use_graph else
                               "stream-ordered launches (no graph), K steps between CUDA events on the launching stream"),
                    "multi_gpu": (f"tensor parallel over {world} ranks: column-parallel 4096x4096 and 4096x16384, row-parallel "
                                  f"16384x4096 with {collectives_per_step} sums of [M,4096] per step, " +
-                                 ("done inside the decode kernel: fp32 partials pushed over NVLink into every rank's exchange buffer, flag hand-shake per CTA"
+                                 ("done inside the decode kernel: fp32 partials pushed over NVLink into every rank's exchange buffer"
                                   if exchange is not None else "NCCL fp16 all-reduce after the kernel")) if world > 1 else "single GPU"},
         "gpu_launches": launches_per_step * args.steps,
+        "step_ms": {"min": step_ms[0], "median": step_ms[len(step_ms) // 2], "max": step_ms[-1], "rank": rank},
         "clocks": clocks,
     }
+    alg = step_bytes / launches_per_step / world
     line["roofline"] = {
         "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
-        # dram__bytes_read+write of one ncu capture (K=4096 N=16384 M=1: 35 707 648 B vs 35 692 544 B algorithmic,
-        # ratio 1.0004; the other shapes stream their weights the same way), scaled to this mix of launches
-        "traffic": 1.0004 * step_bytes / launches_per_step / world, "kernel": "skinny_kernel", "peak_source": f"of {peaks['source']} (copy bandwidth)",
-        "algorithmic_bytes_per_launch": step_bytes / launches_per_step / world,
+        "traffic": TRAFFIC_RATIO * alg, "traffic_source": "profiles/gemv_kernel_step_order_dram_bytes.md (ncu, 12 consecutive launches in the step's order)",
+        "kernel": "gemv_kernel", "peak_source": f"of {peaks['source']} (copy bandwidth)",
+        "algorithmic_bytes_per_launch": alg,
         "avg_launch_us": 1e3 * ms / (args.steps * launches_per_step),
     }
 
-    e2e = None if args.small else e2e_host(lib, weights, dev, stream, sets, world, local_shape)
-    if rank == 0 and not args.small:
+    if world > 1:
+        line["tp_check"] = tp_check(lib, dist, exchange, weights, dev, stream, world, rank, local_shape)
+    if not args.small:
+        e2e = e2e_host(lib, weights, dev, stream, world, local_shape, calls[:4 * len(DECODE_SHAPES) * len(DECODE_M)])
+        if rank == 0:
+            line["e2e"] = e2e
         if world == 1:
-            line["sweep"] = decode_sweep(lib, weights, xs, outs, stream, sets, peaks)
-        line["e2e"] = e2e
-        if not args.no_prefill and world == 1:
-            line["prefill"] = prefill_sweep(lib, weights, dev, stream, sets, peaks)
-        if not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(repeat=5)
+            line["sweep"] = decode_sweep(lib, weights, xs, outs, stream, peaks)
+            if not args.no_prefill:
+                line["prefill"] = prefill_sweep(lib, weights, dev, stream, peaks)
+            if not args.no_ref_kernel:
+                line["ref_kernel"] = ref_kernel_rows(lib, weights, dev, line.get("sweep"), line.get("prefill"))
+    # the sweep's buffers are not needed any more
+    if exchange is not None:
+        exchange.close()
+        exchange = None
+    del weights, xs, outs
+    torch.cuda.empty_cache()
+    if not args.small and not args.no_models:
+        m = model_line(args, "opt-6.7b", rank, world, dev, dist, steps=2)
+        line["model_opt67b"] = {k: m[k] for k in ("value", "unit", "prefill_tokens_per_s", "decode_ms_per_token", "config")}
+        if world > 1:
+            torch.cuda.empty_cache()
+            m = model_line(args, "llama2-7b", rank, world, dev, dist, steps=1)
+            line["model_llama2_7b"] = {k: m[k] for k in ("value", "unit", "prefill_tokens_per_s", "decode_ms_per_token", "config")}
+    if rank == 0 and not args.small and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -435,22 +510,53 @@ def main():
         print(json.dumps(line), flush=True)
 
 
-def run_model(args):
+def tp_check(lib, dist, exchange, weights, dev, stream, world, rank, local_shape):
+    """Outside the timed region: the row-parallel product summed inside the kernel against the same partial products
+    summed by NCCL (GEMM tolerance), and bit-equality of the fused result across the ranks."""
+    if exchange is None:
+        return "skipped: no peer exchange (NCCL route timed)"
+    K, N = 16384, 4096
+    kl, nl, _ = local_shape(K, N)
+    qw, zs = weights[(K, N)][0]
+    sp = stream.cuda_stream
+    verdicts = []
+    for M in (1, 16):
+        x = torch.randn(M, kl, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(77 + rank))
+        fused = torch.empty(M, nl, device=dev, dtype=torch.float16)
+        part = torch.empty(M, nl, device=dev, dtype=torch.float16)
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            r = lib.w4a16_gemm_allreduce(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, fused.data_ptr(), M, nl, kl, G, kl,
+                                         exchange.buffers, world, rank, exchange.capacity, sp, 0)
+            r2 = lib.w4a16_gemm_ex(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, part.data_ptr(), M, nl, kl, G, None, 0, sp, 0, 0)
+        stream.synchronize()
+        if r != 0 or r2 != 0:
+            return f"launch failed: {r} {r2}"
+        total = part.float()
+        dist.all_reduce(total)                                    # fp32 sum of the fp16-rounded partial products
+        scale = float(total.abs().max().clamp_min(1e-6))
+        close = bool(((fused.float() - total).abs().max() / scale) <= 4e-3)
+        ref = fused.clone()
+        dist.broadcast(ref, src=0)
+        same = torch.tensor([int(torch.equal(ref, fused)) & int(close)], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        verdicts.append(int(same.item()))
+    err = exchange.status()[1]
+    if err:
+        return f"peer exchange gave up waiting for rank {err - 1}"
+    return "ok" if all(verdicts) else f"mismatch (M=1: {verdicts[0]}, M=16: {verdicts[1]})"
+
+
+MODEL_WORKLOADS = {"opt-6.7b": (8, 512, 128), "llama2-7b": (32, 1024, 256)}      # batch, prompt tokens, new tokens
+
+
+def model_line(args, workload, rank, world, dev, dist, steps=None):
     """BASELINE configs 4/5: the full decoder stack with every linear W4A16, random init, tensor parallel over
-    the ranks torchrun started.  A step = one prompt batch prefilled + greedy decoding; value = decode tokens/s."""
-    import torch.distributed as dist
+    the ranks torchrun started.  A step = one prompt batch prefilled + greedy decoding; value = decode tokens/s
+    (method of the reference's speed test: tokens / wall time of each phase, synchronised)."""
     from w4a16.models import Decoder, DecoderConfig
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    if args.workload == "opt-6.7b":
-        cfg, batch, prompt, new = DecoderConfig.opt_6_7b(), 8, 512, 128
-    else:
-        cfg, batch, prompt, new = DecoderConfig.llama2_7b(), 32, 1024, 256
+    cfg = DecoderConfig.opt_6_7b() if workload == "opt-6.7b" else DecoderConfig.llama2_7b()
+    batch, prompt, new = MODEL_WORKLOADS[workload]
     if args.layers:
         cfg.layers = args.layers
     exchange = None
@@ -458,18 +564,18 @@ def run_model(args):
         exchange = make_exchange(32 * cfg.hidden, dev, dist)
     model = Decoder(cfg, rank, world, None, dev, seed=1234, exchange=exchange).mark_static()
     ids = torch.randint(0, cfg.vocab, (batch, prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(7))
-    steps, warm = max(1, min(args.steps, 5)), 1
-    # NCCL collectives inside graph capture hung on this pool: with --reduce nccl the TP > 1 token steps run eagerly;
-    # with the fused exchange the step holds no library collective and is captured at any world size
+    steps = max(1, min(args.steps, 5)) if steps is None else steps
+    warm = 1
+    # NCCL collectives are never captured in a graph: with --reduce nccl the token steps of N > 1 run eagerly; with
+    # the fused exchange the step holds no library collective and is captured at any world size
     graphed = (world == 1 or (exchange is not None and batch <= 32)) and args.graph != "off"
-    gen = (lambda n: model.generate_graphed(ids, n, use_graph=True)) if graphed else (lambda n: model.generate_graphed(ids, n, use_graph=False))
     for _ in range(warm):
-        gen(8)
+        model.generate_graphed(ids, 8, use_graph=graphed)
     tp, td = [], []
     for _ in range(steps):
         if world > 1:
             dist.barrier()
-        _, t_prefill, t_decode = gen(new)
+        _, t_prefill, t_decode = model.generate_graphed(ids, new, use_graph=graphed)
         t = torch.tensor([t_prefill, t_decode], device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -478,22 +584,22 @@ def run_model(args):
             raise RuntimeError(f"peer exchange gave up waiting for rank {exchange.status()[1] - 1}")
     prefill_tps = batch * prompt / float(np.mean(tp))
     decode_tps = batch * (new - 1) / float(np.mean(td))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps({
-            "metric": f"{args.workload}_w4a16_decode_tokens_per_s", "value": decode_tps, "unit": "tokens/s", "n_gpus": world,
-            "steps": steps, "warmup": warm, "ms_per_step": 1e3 * float(np.mean(tp) + np.mean(td)), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16xs4->f32", "data": "synthetic (random-init packed weights, random token ids)",
-            "config": {"workload": args.workload, "layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "group_size": cfg.group_size,
-                       "batch": batch, "prompt_tokens": prompt, "new_tokens": new, "parallelism": f"tp{world}",
-                       "attention": "torch scaled_dot_product_attention over a static KV cache (not part of the W4A16 path)",
-                       "decode_loop": "one CUDA graph per token step, replayed" if graphed else "eager token steps",
-                       "row_parallel_sum": "single GPU" if world == 1 else ("inside the decode kernel through peer memory" if exchange is not None and batch <= 32 else "NCCL fp16 all-reduce"),
-                       "timing": "host wall clock around synchronised prefill / decode phases, max over ranks"},
-            "prefill_tokens_per_s": prefill_tps, "decode_ms_per_token": 1e3 * float(np.mean(td)) / (new - 1),
-        }), flush=True)
+    fused = exchange is not None and batch <= 32
+    if exchange is not None:
+        exchange.close()
+    del model
+    return {
+        "metric": f"{workload}_w4a16_decode_tokens_per_s", "value": decode_tps, "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warm, "ms_per_step": 1e3 * float(np.mean(tp) + np.mean(td)), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16xs4->f32", "data": "synthetic (random-init packed weights, random token ids)",
+        "config": {"workload": workload, "layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "group_size": cfg.group_size,
+                   "batch": batch, "prompt_tokens": prompt, "new_tokens": new, "parallelism": f"tp{world}",
+                   "attention": "decode: the library's decode attention kernel over a static KV cache; prefill: torch scaled_dot_product_attention",
+                   "decode_loop": "one CUDA graph per token step, replayed" if graphed else "eager token steps",
+                   "row_parallel_sum": "single GPU" if world == 1 else ("inside the decode kernel through peer memory" if fused else "NCCL fp16 all-reduce"),
+                   "timing": "host wall clock around synchronised prefill / decode phases, max over ranks"},
+        "prefill_tokens_per_s": prefill_tps, "decode_ms_per_token": 1e3 * float(np.mean(td)) / (new - 1),
+    }
 
 
 def run_single(spec):
@@ -509,9 +615,12 @@ def run_single(spec):
     sets = [synth_packed(K, N, G, dev, 100 + s) for s in range(4)]
     x = torch.randn(M, K, device=dev, dtype=torch.float16)
     o = torch.empty(M, N, device=dev, dtype=torch.float16)
+    ws_bytes = lib.w4a16_workspace_bytes(M, N, K, G) if algo != 1 else 0
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
     for i in range(reps):
         qw, zs = sets[i % 4]
-        r = lib.w4a16_gemm_algo(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G, None, 0, None, algo)
+        r = lib.w4a16_gemm_algo(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G,
+                                ws.data_ptr() if ws_bytes else None, ws_bytes, None, algo)
         if r != 0:
             raise RuntimeError(lib.w4a16_status_str(r).decode())
     torch.cuda.synchronize()
@@ -540,20 +649,23 @@ def run_single_attention(spec):
 
 
 def time_calls(fn, stream, iters, warm=5):
+    """(median, min) ms per call over `iters` calls, each between its own pair of CUDA events on `stream`."""
     with torch.cuda.stream(stream):
         for i in range(warm):
             fn(i)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        ev[0].record(stream)
         for i in range(iters):
             fn(i)
-        e1.record(stream)
+            ev[i + 1].record(stream)
     stream.synchronize()
-    return e0.elapsed_time(e1) / iters      # ms per call
+    t = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(iters))
+    return t[len(t) // 2], t[0]
 
 
-def time_graph(fn, stream, launches, replays):
-    """ms per launch of `launches` calls captured in one CUDA graph (no host launch cost), rotating weight sets."""
+def time_graph(fn, stream, launches, replays=7):
+    """(median, min) ms per launch of `launches` calls captured in one CUDA graph (no host launch cost) over
+    `replays` replays, each between its own pair of CUDA events."""
     with torch.cuda.stream(stream):
         fn(0)
     stream.synchronize()
@@ -564,35 +676,50 @@ def time_graph(fn, stream, launches, replays):
     with torch.cuda.stream(stream):
         for _ in range(3):
             g.replay()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(replays):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+        ev[0].record(stream)
+        for i in range(replays):
             g.replay()
-        e1.record(stream)
+            ev[i + 1].record(stream)
     stream.synchronize()
-    return e0.elapsed_time(e1) / (replays * launches)
+    t = sorted(ev[i].elapsed_time(ev[i + 1]) / launches for i in range(replays))
+    return t[len(t) // 2], t[0]
 
 
-def decode_sweep(lib, weights, xs, outs, stream, sets, peaks):
-    """Per (shape, M): back-to-back launches inside a CUDA graph, rotating over the weight sets."""
+def decode_sweep(lib, weights, xs, outs, stream, peaks):
+    """Per (shape, M): back-to-back launches inside a CUDA graph, rotating over all weight sets of the shape
+    (2 x L2 or more of distinct bytes between two uses of a set); median and minimum over 7 replays.  `single_us` is
+    the latency of one isolated launch (stream idle before and after)."""
     rows = []
     sp = stream.cuda_stream
     for (K, N) in DECODE_SHAPES:
+        sets = weights[(K, N)]
         for M in DECODE_M:
-            def fn(i, sp=sp, M=M, K=K, N=N):
-                qw, zs = weights[(K, N)][i % sets]
+            def fn(i, sp=sp, M=M, K=K, N=N, sets=sets):
+                qw, zs = sets[i % len(sets)]
                 lib.w4a16_gemm_ex(xs[(M, K, N)].data_ptr(), qw.data_ptr(), zs.data_ptr(), None, outs[(M, K, N)].data_ptr(),
                                   M, N, K, G, None, 0, sp, 0, 1)
-            ms = time_graph(fn, stream, 5 * sets, 10)
-            gbs = decode_bytes(M, K, N) / (ms * 1e-3) / 1e9
-            rows.append({"K": K, "N": N, "M": M, "us": 1e3 * ms, "GBps": gbs, "frac": gbs / peaks["hbm_gbs"]})
+            med, mn = time_graph(fn, stream, len(sets))
+            singles = []
+            for i in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                stream.synchronize()
+                with torch.cuda.stream(stream):
+                    e0.record(stream)
+                    fn(i + 1)
+                    e1.record(stream)
+                stream.synchronize()
+                singles.append(e0.elapsed_time(e1))
+            gbs = decode_bytes(M, K, N) / (med * 1e-3) / 1e9
+            rows.append({"K": K, "N": N, "M": M, "us": 1e3 * med, "us_min": 1e3 * mn, "GBps": gbs, "frac": gbs / peaks["hbm_gbs"],
+                         "single_us": 1e3 * sorted(singles)[len(singles) // 2], "weight_sets": len(sets)})
     return rows
 
 
-def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
-    """The same sweep through w4a16_gemm_host: x from pinned host memory, y back to pinned host memory,
-    both copies inside the timed region; the packed weights stay resident (module state).  With several
-    ranks every rank runs its shard through the host-buffer call (rank 0 reports; no collective here)."""
+def e2e_host(lib, weights, dev, stream, world, local_shape, calls):
+    """The sweep through w4a16_gemm_host: x from pinned host memory, y back to pinned host memory, both copies inside
+    the timed region; the packed weights stay resident (module state).  With several ranks every rank runs its shard
+    through the host-buffer call (rank 0 reports; no collective here).  One step here = `calls` (4 rounds)."""
     sp = stream.cuda_stream
     xh, oh, xd, od = {}, {}, {}, {}
     for (K, N) in DECODE_SHAPES:
@@ -602,7 +729,6 @@ def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
             oh[(M, K, N)] = torch.empty(M, nl, dtype=torch.float16).pin_memory()
             xd[(M, K, N)] = torch.empty(M, kl, dtype=torch.float16, device=dev)
             od[(M, K, N)] = torch.empty(M, nl, dtype=torch.float16, device=dev)
-    calls = [(M, K, N, s) for s in range(sets) for (K, N) in DECODE_SHAPES for M in DECODE_M]
 
     n_lanes = int(os.environ.get("W4A16_E2E_STREAMS", "4"))
     sides = [torch.cuda.Stream(device=dev) for _ in range(max(1, n_lanes) - 1)]
@@ -637,7 +763,7 @@ def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
     stream.synchronize()
     wall_sync = time.perf_counter() - t0
     dev_ms = e0.elapsed_time(e1) / steps
-    # (b) the step as a batch: every call's copy-in, GEMM and copy-out enqueued with w4a16_gemm_host_async on two
+    # (b) the step as a batch: every call's copy-in, GEMM and copy-out enqueued with w4a16_gemm_host_async on a few
     # streams, ONE synchronisation per step before the results are read
     for c in calls:
         one(c, lib.w4a16_gemm_host_async, lanes[lane_of[c[:3]]])
@@ -651,39 +777,111 @@ def e2e_host(lib, weights, dev, stream, sets, world, local_shape):
             s_.synchronize()
     wall = time.perf_counter() - t0
     return {"value": step_bytes * steps / wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "steps": steps, "ms_per_step": 1e3 * wall / steps,
+            "steps": steps, "ms_per_step": 1e3 * wall / steps, "launches_per_step": len(calls),
             "timer": f"host wall clock; per step: all calls enqueued through w4a16_gemm_host_async (pinned host x in, y out) on {len(lanes)} streams, one synchronisation",
             "per_call_sync": {"value": step_bytes * steps / wall_sync / 1e9, "ms_per_step": 1e3 * wall_sync / steps,
                               "device_event_ms_per_step": dev_ms,
                               "what": "w4a16_gemm_host: every call synchronises before it returns"}}
 
 
-def prefill_sweep(lib, weights, dev, stream, sets, peaks):
-    """tcgen05 GEMM: TFLOP/s = 2*M*N*K / time for M in {512, 2048, 8192} on the three shapes."""
+def prefill_sweep(lib, weights, dev, stream, peaks):
+    """tcgen05 GEMM: TFLOP/s = 2*M*N*K / time for M in {512, 2048, 8192} on the three shapes; median and minimum over
+    20 calls, each between its own CUDA events, rotating over the weight sets."""
     rows = []
     sp = stream.cuda_stream
     for (K, N) in DECODE_SHAPES:
+        sets = weights[(K, N)]
         for M in PREFILL_M:
             x = torch.randn(M, K, device=dev, dtype=torch.float16)
             o = torch.empty(M, N, device=dev, dtype=torch.float16)
             ws_bytes = lib.w4a16_workspace_bytes(M, N, K, G)          # > 0 when the library wants to split K
             ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
 
-            def fn(i, M=M, K=K, N=N, x=x, o=o, ws=ws, ws_bytes=ws_bytes):
-                qw, zs = weights[(K, N)][i % sets]
+            def fn(i, M=M, K=K, N=N, x=x, o=o, ws=ws, ws_bytes=ws_bytes, sets=sets):
+                qw, zs = sets[i % len(sets)]
                 r = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G,
                                    ws.data_ptr() if ws_bytes else None, ws_bytes, sp)
                 if r != 0:
                     raise RuntimeError(lib.w4a16_status_str(r).decode())
-            ms = time_calls(fn, stream, 20, warm=3)
-            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
-            rows.append({"K": K, "N": N, "M": M, "ms": ms, "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+            med, mn = time_calls(fn, stream, 20, warm=3)
+            tf = 2.0 * M * N * K / (med * 1e-3) / 1e12
+            rows.append({"K": K, "N": N, "M": M, "ms": med, "ms_min": mn, "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                          "frac_of_nominal_2250": tf / 2250.0, "workspace_bytes": ws_bytes})
             del x, o, ws
     flag = ctypes.c_int(0)
     lib.w4a16_device_error_flag(ctypes.byref(flag))
     return {"rows": rows, "kernel": "tc_kernel (TMA + tcgen05.mma, A from TMEM)", "timeout_flag": flag.value,
             "peak_tflops_measured_bf16_burst": peaks["bf16_tflops"]}
+
+
+def ref_kernel_rows(lib, weights, dev, sweep_rows, prefill):
+    """The reference's own CUDA kernel (gemm_s4_f16_nn, g = 128), rebuilt unmodified for sm_100a by oracle/build_ref.py,
+    timed on this GPU next to the numbers above: a same-box comparator, outside every timed region of the product.  It
+    launches on the legacy default stream and allocates its output per call, so it is timed as the reference runs it:
+    stream-ordered calls between CUDA events on that stream, rotating over the same weight sets.  A row is only timed
+    when the kernel's output agrees with this library's on every token row (rebuilt for sm_100a it returns wrong rows
+    for some tile configurations); otherwise the row says so."""
+    so = glob.glob(os.path.join(ROOT, "oracle", "_ref", "quant*.so"))
+    if not so:
+        return {"unavailable": "reference extension not built (oracle/build_ref.py needs the reference tree)"}
+    try:
+        spec = importlib.util.spec_from_file_location("quant", so[0])
+        refq = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(refq)
+    except Exception as e:                                    # noqa: BLE001
+        return {"unavailable": f"reference extension does not load: {e}"}
+    mine = {}
+    for r in (sweep_rows or []):
+        mine[(r["K"], r["N"], r["M"])] = r["us"]
+    for r in ((prefill or {}).get("rows") or []):
+        mine[(r["K"], r["N"], r["M"])] = 1e3 * r["ms"]
+    default = torch.cuda.default_stream(dev)
+    rows = []
+    for (K, N) in DECODE_SHAPES:
+        sets = weights[(K, N)]
+        for M in (1, 4, 8, 16, 512, 2048):
+            x = torch.randn(1, M, K, device=dev, dtype=torch.float16)
+            qw, zs = sets[0]
+            with torch.cuda.stream(default):
+                ref = refq.gemm_awq_ut(x, qw, zs, M, N, K, G)
+            torch.cuda.synchronize()
+            own = torch.empty(1, M, N, device=dev, dtype=torch.float16)
+            ws_bytes = lib.w4a16_workspace_bytes(M, N, K, G)
+            ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+            st = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, own.data_ptr(), M, N, K, G,
+                                ws.data_ptr() if ws_bytes else None, ws_bytes, None)
+            torch.cuda.synchronize()
+            bound = 1e-2 * float(x.abs().max()) * math.sqrt(K) * 0.1           # max |w| of the synthetic weights is ~ 0.1
+            bad = int(((ref[0].float() - own[0].float()).abs().amax(dim=1) > bound).sum()) if st == 0 else M
+            row = {"K": K, "N": N, "M": M}
+            if bad:
+                row.update({"us": None, "note": f"wrong rows on sm_100a: {bad} of {M} token rows disagree with this library beyond the GEMM tolerance"})
+            else:
+                reps = 40 if M <= 16 else 10
+                with torch.cuda.stream(default):
+                    for i in range(3):
+                        refq.gemm_awq_ut(x, *sets[i % len(sets)], M, N, K, G)
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+                    ev[0].record(default)
+                    for i in range(reps):
+                        refq.gemm_awq_ut(x, *sets[i % len(sets)], M, N, K, G)
+                        ev[i + 1].record(default)
+                torch.cuda.synchronize()
+                t = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(reps))
+                us = 1e3 * t[len(t) // 2]
+                row.update({"us": us, "us_min": 1e3 * t[0]})
+                if M <= 16:
+                    row["GBps"] = decode_bytes(M, K, N) / us / 1e3
+                else:
+                    row["TFLOPs"] = 2.0 * M * N * K / us / 1e6
+                if (K, N, M) in mine:
+                    row["this_library_us"] = mine[(K, N, M)]
+                    row["speedup"] = us / mine[(K, N, M)]
+            rows.append(row)
+            del x, ref, own, ws
+    return {"kernel": "gemm_s4_f16_nn (mma.sync + cp.async, rebuilt unmodified for sm_100a; oracle/_ref)",
+            "timing": "stream-ordered calls on the legacy default stream between CUDA events, median; includes the per-call "
+                      "torch::empty and tile selection of the reference's host path", "rows": rows}
 
 
 if __name__ == "__main__":

@@ -44,8 +44,8 @@ typedef enum w4a16_status {
 
 /* kernel selection for w4a16_gemm_algo */
 typedef enum w4a16_algo {
-    W4A16_ALGO_AUTO   = 0,  /* tokens <= 32: skinny kernel; otherwise the tcgen05 kernel */
-    W4A16_ALGO_SKINNY = 1,  /* mma.sync skinny GEMM, cluster split-K (decode) */
+    W4A16_ALGO_AUTO   = 0,  /* tokens <= 32: decode kernels; otherwise the tcgen05 kernel */
+    W4A16_ALGO_SKINNY = 1,  /* mma.sync decode kernels (up to 8 tokens: two CTAs per SM; up to 32: cluster split-K) */
     W4A16_ALGO_TC     = 2   /* TMA + tcgen05/TMEM GEMM (prefill) */
 } w4a16_algo;
 
@@ -255,21 +255,46 @@ int w4a16_static_scratch_error_flag(int* flag);
  */
 int w4a16_device_error_flag(int* flag);
 
+/* Clears the per-device error word (synchronises the device).  After a kernel gave up on a wait the word stays set
+ * until this call; the reference has no counterpart. */
+int w4a16_device_error_clear(void);
+
+/* Clears the `gave up` mark and the arrival counter of an exchange buffer (w4a16_exchange_alloc) after a wait for a
+ * peer ran out, so that later calls wait for their peers again.  Synchronises the device; call it on every rank
+ * before the ranks resume calling.  No counterpart in the reference. */
+int w4a16_exchange_reset(void* buffer);
+
+/* How long a kernel waits for a peer's partial sums in the exchange buffers before it gives up, in milliseconds
+ * (0 restores the default of 2000).  Process-wide; applies to launches made after the call. */
+void w4a16_tune_exchange_wait(unsigned milliseconds);
+
 /* Debug aid: runs a one-CTA probe that writes tagged words to tensor memory with the 16-lane
  * fragment store the tcgen05 kernel uses and reads them back lane by lane; out = uint32
  * [128 lanes][32 columns] on the device.  tests/test_gpu_tmem.py decodes it. */
 int w4a16_debug_tmem_layout(void* out, void* stream);
 
-/* Debug aid: device buffer of uint64 [CTAs][16 warps][8] that receives %globaltimer stamps of
- * the skinny kernel's phases (start, x staged, after barrier, first weights landed, main loop
- * done, partials visible, cluster barrier passed, end); NULL switches it off. */
+/* Debug aid (library built with -DW4A16_SKINNY_DEBUG): device buffer of uint64 [CTAs][16 warps][8] that receives
+ * %globaltimer stamps of the decode kernels' phases; NULL switches it off.  8-token kernel: start, previous grid
+ * complete, first unit landed, main loop done, partial sums visible, end. */
 void w4a16_debug_skinny_timeline(void* buf);
 
 /* Benchmark/tuning hooks, not part of the drop-in surface (0 = automatic choice):
- * skinny kernel: out-feature tiles per CTA (1,2,4,8) and cluster split-K (1,2,4,8);
- * tcgen05 kernel: token tile (64,128,256). */
+ * 16-warp decode kernel: out-feature tiles per CTA (1,2,4,8,16) and cluster split-K (1..8);
+ * tcgen05 kernel: token tile (64,128,256) and K parts per output tile;
+ * decode path: kernel (1 = the kernel for up to 32 tokens per pass, 2 = the kernel for up to 8 tokens per pass,
+ * 0 = by token count), and for the 8-token kernel out-feature tiles per CTA (1,2,4,8,16), cluster split-K (1..8)
+ * and ring depth (2..4). */
 void w4a16_tune_skinny(int wn, int splits);
 void w4a16_tune_tc(int tile_tokens, int split_k);
+void w4a16_tune_decode(int kernel, int tiles_per_cta, int splits, int depth);
+/* 8-token decode kernel: how many 128-k units beyond its shared-memory ring each warp prefetches into L2
+ * (negative = automatic). */
+void w4a16_tune_decode_prefetch(int units_ahead);
+
+/* Debug aid: the launch shape the 8-token decode kernel would use for a problem, without launching:
+ * plan9 = {tokens per pass, out-feature tiles per CTA, cluster size, ring depth, rows per activation box,
+ * shared memory bytes, CTAs with work along x, grid y, grid z} (host array). */
+int w4a16_debug_decode_plan(int tokens, int N, int K, int group_size, int* plan9);
 
 /* Number of kernels this library has launched on the calling process so far. */
 unsigned long long w4a16_launch_count(void);

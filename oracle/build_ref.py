@@ -14,6 +14,13 @@ That module is a GPU comparator for the parity tests (layout kernels byte-for-by
 identity-matrix dequant trick, GEMM outputs) and the generator of the golden vectors under
 tests/golden/.  It is never imported by the product.
 
+It also stages, unmodified and again only into the untracked oracle/_ref/, the three Python
+files of the reference that sit directly on top of the `quant` extension
+(test/nvidia/module/qlinear/qlinear.py, test/nvidia/utils/quant_dequant_nvidia.py,
+test/nvidia/utils/quant_funcs.py) under oracle/_ref/refpy/ with their package layout, so that
+tests/test_gpu_dropin_reference_python.py can run the reference's own WALinear on this
+library's `quant` module.
+
 Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--jobs 4]
 Exits 0 and does nothing if the reference tree is absent (the GPU box only uses the
 prebuilt file) or the module is already built and newer than its sources.
@@ -35,6 +42,32 @@ SOURCES = [
 ]
 
 
+PY_FILES = [
+    "module/qlinear/qlinear.py",
+    "utils/quant_dequant_nvidia.py",
+    "utils/quant_funcs.py",
+]
+
+
+def stage_python(reference, verbose=True):
+    """Copy the reference's WALinear and quantizer Python (unmodified) to oracle/_ref/refpy/."""
+    import shutil
+    src_root = os.path.join(reference, "test", "nvidia")
+    if not os.path.isdir(src_root):
+        return None
+    dst_root = os.path.join(OUT, "refpy")
+    for rel in PY_FILES:
+        src, dst = os.path.join(src_root, rel), os.path.join(dst_root, rel)
+        if not os.path.exists(src):
+            if verbose:
+                print(f"[build_ref] missing {src}")
+            return None
+        os.makedirs(os.path.dirname(dst), exist_ok=True)
+        if not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(src):
+            shutil.copyfile(src, dst)
+    return dst_root
+
+
 def target_path():
     return os.path.join(OUT, "quant" + sysconfig.get_config_var("EXT_SUFFIX"))
 
@@ -47,6 +80,7 @@ def build(reference, jobs=4, verbose=True):
         return None
     srcs = [os.path.join(src_root, s) for s in SOURCES]
     tgt = target_path()
+    stage_python(reference, verbose)
     if os.path.exists(tgt) and all(os.path.getmtime(tgt) >= os.path.getmtime(s) for s in srcs):
         if verbose:
             print(f"[build_ref] up to date: {tgt}")
@@ -98,8 +132,12 @@ def build(reference, jobs=4, verbose=True):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("W4A16_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("W4A16_REFERENCE", ""),
+                    help="root of the reference tree (or set W4A16_REFERENCE)")
     ap.add_argument("--jobs", type=int, default=4)
     a = ap.parse_args()
+    if not a.reference:
+        print("[build_ref] no reference tree given (--reference or W4A16_REFERENCE); nothing to do")
+        sys.exit(0)
     build(a.reference, a.jobs)
     sys.exit(0)

@@ -1,5 +1,6 @@
 // C-ABI entry points: argument validation, kernel selection, error bookkeeping.
 #include <atomic>
+#include <mutex>
 
 #include <cuda.h>
 
@@ -24,16 +25,19 @@ bool aux_programmatic_launch() { return g_aux_programmatic.load(std::memory_orde
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-// Allocated once per device (first use; outside stream capture), never freed, only ever set to 1.
+// Allocated once per device (first use; outside stream capture), never freed.  Word 0 is the error word (only ever
+// raised by kernels, cleared by w4a16_device_error_clear); word 1 is a generation counter the decode kernel bumps.
 int* device_error_word()
 {
     static int* words[64] = {nullptr};
+    static std::mutex lock;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> guard(lock);
     if (!words[dev]) {
         int* p = nullptr;
-        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-        if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return nullptr;
+        if (cudaMalloc(&p, 64) != cudaSuccess) return nullptr;
+        if (cudaMemset(p, 0, 64) != cudaSuccess) return nullptr;
         words[dev] = p;
     }
     return words[dev];
@@ -78,6 +82,11 @@ int encode_tensor_map_2d(void* tmap, const void* base, int elem_bytes, const uin
 
 void skinny_force_config(int wn, int splits);
 void skinny_set_timeline(unsigned long long* buf);
+void gemv_force_config(int tn, int splits, int depth);
+void gemv_set_timeline(unsigned long long* buf);
+void decode_force_kernel(int which);
+int gemv_plan(int tokens, int N, int K, int g, int* plan);
+void gemv_force_ahead(int units);
 void tc_force_config(int tile_tokens, int split_k);
 
 namespace {
@@ -189,9 +198,11 @@ int gemm_host_impl(const void* x_host, void* out_host, void* x_dev, void* out_de
                    const void* zeros_scales, const void* bias, int tokens, int N, int K, int group_size,
                    void* workspace, size_t workspace_bytes, void* stream, bool sync)
 {
-    if (tokens < 0) return W4A16_ERR_BAD_SHAPE;
+    if (!x_host || !out_host || !x_dev || !out_dev) return tokens == 0 ? W4A16_OK : W4A16_ERR_NULL_POINTER;
+    // every argument is checked before the first copy is enqueued
+    int v = validate(x_dev, qweight, zeros_scales, out_dev, tokens, N, K, group_size);
+    if (v != W4A16_OK) return v;
     if (tokens == 0) return W4A16_OK;
-    if (!x_host || !out_host || !x_dev || !out_dev) return W4A16_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemcpyAsync(x_dev, x_host, (size_t)tokens * K * sizeof(__half), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return record_cuda_error(e);
@@ -230,10 +241,35 @@ extern "C" int w4a16_device_error_flag(int* flag)
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
 
+extern "C" int w4a16_device_error_clear(void)
+{
+    int* w = device_error_word();
+    if (!w) return W4A16_ERR_CUDA;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemset(w, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
 // Tuning hooks for benchmarks (0 = automatic).  Not part of the drop-in surface.
 extern "C" void w4a16_tune_skinny(int wn, int splits) { skinny_force_config(wn, splits); }
-// Debug aid: device buffer [ctas][16 warps][8] receiving %globaltimer stamps of the skinny kernel's phases (NULL = off).
-extern "C" void w4a16_debug_skinny_timeline(void* buf) { skinny_set_timeline((unsigned long long*)buf); }
+extern "C" void w4a16_tune_decode(int kernel, int tiles_per_cta, int splits, int depth)
+{
+    decode_force_kernel(kernel);
+    gemv_force_config(tiles_per_cta, splits, depth);
+}
+extern "C" void w4a16_tune_decode_prefetch(int units_ahead) { gemv_force_ahead(units_ahead); }
+extern "C" int w4a16_debug_decode_plan(int tokens, int N, int K, int group_size, int* plan9)
+{
+    if (!plan9) return W4A16_ERR_NULL_POINTER;
+    return gemv_plan(tokens, N, K, group_size, plan9);
+}
+// Debug aid: device buffer [ctas][16 warps][8] receiving %globaltimer stamps of the decode kernels' phases (NULL = off).
+extern "C" void w4a16_debug_skinny_timeline(void* buf)
+{
+    skinny_set_timeline((unsigned long long*)buf);
+    gemv_set_timeline((unsigned long long*)buf);
+}
 extern "C" void w4a16_tune_tc(int tile_tokens, int split_k) { tc_force_config(tile_tokens, split_k); }
 // 1: the small decode-step kernels (attention, add+norm, SwiGLU product, exchange all-gather) are launched with
 // programmatic stream serialization; 0 (default): plain stream order - measured faster (OPT-6.7B-shaped step 1.8 %,

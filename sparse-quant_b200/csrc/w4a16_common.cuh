@@ -193,7 +193,11 @@ int* device_error_word();
 int encode_tensor_map_2d(void* tmap, const void* base, int elem_bytes, const uint64_t dims[2], uint64_t row_stride_bytes,
                          const uint32_t box[2], bool swizzle128);                       // per-device word a kernel sets to 1 when a bounded wait gives up
 
+// decode path: tokens <= 16 per pass -> launch_gemv (8-warp CTAs, two per SM), otherwise the 16-warp kernel
 int launch_skinny(const GemmArgs& a, cudaStream_t st);
+int launch_gemv(const GemmArgs& a, cudaStream_t st);
+// how long a kernel waits for a peer's partial sums in the exchange buffers before it gives up (w4a16_tune_exchange_wait)
+unsigned long long exchange_wait_budget_ns();
 // err_word: device word raised on a barrier timeout (nullptr = the library's per-device word)
 // force_split: 0 = planned, otherwise the number of K parts per output tile
 int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st, int* err_word = nullptr,

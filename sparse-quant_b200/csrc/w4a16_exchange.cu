@@ -9,9 +9,16 @@
 //
 // The buffers are ordinary device allocations shared through CUDA IPC: w4a16_exchange_alloc on every rank, the
 // 64-byte handles exchanged by the host program (any transport), w4a16_exchange_open on every peer handle.
+#include <atomic>
+#include <cstddef>
 #include <cstring>
 
 #include "w4a16_common.cuh"
+
+namespace w4a16 {
+static std::atomic<unsigned long long> g_peer_wait_ns{2000ull * 1000 * 1000};
+unsigned long long exchange_wait_budget_ns() { return g_peer_wait_ns.load(std::memory_order_relaxed); }
+}  // namespace w4a16
 
 using namespace w4a16;
 
@@ -32,6 +39,7 @@ struct GatherParams {
     int* error;
     int words, world, rank;
     long long capacity;
+    unsigned long long wait_budget_ns;
 };
 
 // All-gather of a few 32-bit words per rank through the exchange buffers (one CTA): write (word, tag) into slot
@@ -63,10 +71,10 @@ __global__ void __launch_bounds__(256) exchange_allgather_kernel(const GatherPar
         for (unsigned polls = 0;; ++polls) {
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(slot) : "memory");
             if (v.y == tag || dead) break;
-            if ((polls & 255u) == 255u) {
+            if ((polls & 63u) == 63u) {
                 const unsigned long long now = timer_ns();
                 if (t0 == 0) t0 = now;
-                if (now - t0 > 2000000000ull) {
+                if (now - t0 > p.wait_budget_ns) {
                     atomicExch(p.error, 2);
                     atomicExch(&hdr->error, 1 + src);
                     dead = true;
@@ -150,6 +158,20 @@ extern "C" int w4a16_exchange_status(const void* buffer, unsigned* epoch, int* e
     return W4A16_OK;
 }
 
+extern "C" int w4a16_exchange_reset(void* buffer)
+{
+    if (!buffer) return W4A16_ERR_NULL_POINTER;
+    cudaError_t e = cudaDeviceSynchronize();                 // no call may be using the buffer
+    if (e == cudaSuccess) e = cudaMemset((unsigned char*)buffer + offsetof(ExchangeHeader, ticket), 0, sizeof(unsigned) + sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
+}
+
+extern "C" void w4a16_tune_exchange_wait(unsigned milliseconds)
+{
+    g_peer_wait_ns.store(milliseconds ? (unsigned long long)milliseconds * 1000000ull : 2000ull * 1000 * 1000, std::memory_order_relaxed);
+}
+
 extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
                                     void* out, int tokens, int N, int K, int group_size, int k_config,
                                     void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
@@ -198,6 +220,7 @@ extern "C" int w4a16_exchange_allgather(const void* in, void* out, int words, vo
     p.error = device_error_word();
     if (!p.error) return W4A16_ERR_CUDA;
     p.words = words; p.world = world; p.rank = rank; p.capacity = (long long)capacity_elems;
+    p.wait_budget_ns = exchange_wait_budget_ns();
     cudaError_t e = launch_after_previous(exchange_allgather_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, p);
     count_launch();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);

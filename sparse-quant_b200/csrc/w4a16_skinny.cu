@@ -89,6 +89,7 @@ struct SkinnyParams {
     unsigned char* self;          // = peer[rank]
     int world, rank;
     long long capacity;
+    unsigned long long wait_budget_ns;   // how long the exchange waits for a peer
     unsigned long long* timeline;   // debug: [cta][warp][8] globaltimer stamps, or null
     int debug_mode;  // experiments: bit 0 = skip the MMA work, bit 1 = skip staging the activations
 };
@@ -206,7 +207,6 @@ __device__ __forceinline__ uint2 ld_slot(const uint2* p)
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
-constexpr uint64_t kPeerWaitBudgetNs = 2000ull * 1000 * 1000;     // a peer that does not show up within 2 s is given up on
 
 // fp32 load from the shared memory of CTA `rank` of this cluster (own rank included)
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank)
@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                 if ((polls & 255u) == 255u) {
                     const uint64_t now = globaltimer_ns();
                     if (t0 == 0) t0 = now;
-                    if (now - t0 > kPeerWaitBudgetNs) {
+                    if (now - t0 > p.wait_budget_ns) {
                         int late = 0;
 #pragma unroll
                         for (int src = 0; src < kExchangeMaxWorld; ++src)
@@ -727,9 +727,13 @@ void skinny_force_config(int wn, int splits)
     g_force_warps = (splits >> 16) & 0xff;
 }
 
+int g_decode_kernel = 0;      // 0: by token count, 1: always the 16-warp kernel, 2: always the 8-warp kernel
+void decode_force_kernel(int which) { g_decode_kernel = which; }
+
 int launch_skinny(const GemmArgs& a, cudaStream_t st)
 {
     if (a.tokens == 0) return W4A16_OK;
+    if (g_decode_kernel == 2 || (g_decode_kernel == 0 && a.tokens <= 8)) return launch_gemv(a, st);
     // with the fused exchange every rank must launch the same shape: choose it from the K all ranks agreed on
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
     if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;
@@ -751,7 +755,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     p.x = a.x; p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out;
     p.error = device_error_word();
     if (!p.error) return W4A16_ERR_CUDA;
-    p.world = 0; p.rank = 0; p.capacity = 0; p.self = nullptr;
+    p.world = 0; p.rank = 0; p.capacity = 0; p.self = nullptr; p.wait_budget_ns = exchange_wait_budget_ns();
     for (int d = 0; d < kExchangeMaxWorld; ++d) p.peer[d] = nullptr;
     if (a.exchange) {
         const ExchangeArgs& x = *a.exchange;

@@ -25,6 +25,8 @@
 //            fp32 -> fp16, bias add, transposed store to out[token, out-feature].
 // Every mbarrier wait is bounded; on a timeout the CTA raises an error word in global memory,
 // drains and frees its tensor memory, and returns.
+#include <mutex>
+
 #include <cuda.h>
 
 #include "w4a16_common.cuh"
@@ -561,12 +563,15 @@ extern "C" int w4a16_gemm_static_scratch(const void* x, const void* qweight, con
     if ((size_t)2 * tokens * N * sizeof(float) > kStaticPartialBytes) return W4A16_ERR_TOO_LARGE;
     if ((long long)((N + kBlockN - 1) / kBlockN) * ((tokens + 63) / 64) > kStaticMaxTiles) return W4A16_ERR_TOO_LARGE;
 
-    // once per device: resolve the device address of the file-scope array (the host-side name is not an address)
+    // once per device: resolve the device address of the file-scope array (the host-side name is not an address).
+    // Host threads making their first call on a device together take turns here, so the set-up runs once.
     static unsigned char* base[64] = {nullptr};
+    static std::mutex setup_lock;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return record_cuda_error(e);
     if (dev < 0 || dev >= 64) return W4A16_ERR_UNSUPPORTED_GPU;
+    std::lock_guard<std::mutex> guard(setup_lock);
     if (!base[dev]) {
         int major = 0;
         e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);

@@ -69,6 +69,12 @@ C_ABI = {
     "w4a16_debug_skinny_timeline": (None, [_vp]),
     "w4a16_tune_skinny": (None, [_ci, _ci]),
     "w4a16_tune_tc": (None, [_ci, _ci]),
+    "w4a16_tune_decode": (None, [_ci, _ci, _ci, _ci]),
+    "w4a16_tune_decode_prefetch": (None, [_ci]),
+    "w4a16_debug_decode_plan": (_ci, [_ci, _ci, _ci, _ci, ctypes.POINTER(_ci)]),
+    "w4a16_device_error_clear": (_ci, []),
+    "w4a16_exchange_reset": (_ci, [_vp]),
+    "w4a16_tune_exchange_wait": (None, [ctypes.c_uint]),
 }
 
 

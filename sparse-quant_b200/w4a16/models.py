@@ -304,6 +304,10 @@ class Decoder(nn.Module):
         Returns (tokens, prefill seconds, decode seconds)."""
         import time
         B, S = prompt_ids.shape
+        if use_graph and self.world > 1 and (self.exchange is None or B > 32):
+            # the step would then hold NCCL collectives (row-parallel sums, logit gather): those are never captured
+            # here - the token steps run eagerly instead
+            use_graph = False
         max_len = S + new_tokens
         self.reset(B, max_len)
         dev = self.device

@@ -112,7 +112,7 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--gpu", action="store_true")
-    ap.add_argument("--reference", default=os.environ.get("W4A16_REFERENCE", "/root/reference"),
+    ap.add_argument("--reference", default=os.environ.get("W4A16_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"),
                     help="checkout of the reference project (CPU stage only)")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"),
                     help="directory that receives golden_reference_cuda.npz (GPU stage)")

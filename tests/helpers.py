@@ -48,3 +48,29 @@ def check_gemm_tolerance(out, ref, x, w_deq, K):
     assert fro <= 2e-3, f"relative Frobenius error {fro} > 2e-3"
     assert torch.allclose(out, ref, atol=2e-2, rtol=2e-2)
     return err, fro
+
+
+def check_gemm_sampled(out, x, p, bias=None, n_tok=16, n_out=48, seed=99):
+    """The same tolerances on a seeded sample of token rows x out-feature columns (>= 256 outputs), for problems
+    whose full oracle product would take minutes on the CPU: out torch [M, N] (device), x torch fp16 [1, M, K],
+    p a make_packed() dict, bias torch fp16 [1, N] or None."""
+    rng = np.random.default_rng(seed)
+    M, N = out.shape
+    toks = np.sort(rng.choice(M, size=min(n_tok, M), replace=False))
+    cols = np.sort(rng.choice(N, size=min(n_out, N), replace=False))
+    xs = x[:, torch.from_numpy(toks)].contiguous()
+    ws = np.ascontiguousarray(p["w_deq"][cols])
+    bs = None if bias is None else bias[:, torch.from_numpy(cols)].contiguous()
+    ref = oracle.gemm_f16(xs, ws, bs).astype(np.float32)
+    got = out[torch.from_numpy(toks).to(out.device)][:, torch.from_numpy(cols).to(out.device)]
+    # the bound uses the norms of the whole problem, as the full check does
+    xmax = float(x.float().abs().max())
+    wmax = float(np.abs(p["w_deq"].astype(np.float32)).max())
+    got = got.float().cpu()
+    ref_t = torch.from_numpy(ref).reshape(got.shape)
+    err = (got - ref_t).abs().max().item()
+    fro = ((got - ref_t).norm() / ref_t.norm().clamp_min(1e-12)).item()
+    assert err <= 1e-2 * xmax * math.sqrt(p["K"]) * wmax + 1e-6, f"max abs err {err}"
+    assert fro <= 2e-3, f"relative Frobenius error {fro} > 2e-3"
+    assert torch.allclose(got, ref_t, atol=2e-2, rtol=2e-2)
+    return err, fro

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import check_gemm_tolerance, make_packed, make_x, to_dev
+from helpers import check_gemm_sampled, check_gemm_tolerance, make_packed, make_x, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -58,21 +58,66 @@ def test_skinny_many_tokens_fallback(M):
 
 
 @pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 16384), (16384, 4096)])
-@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("M", [1, 4, 8, 16])
 def test_skinny_opt_shapes(K, N, M):
+    """The decode sweep of the benchmark: every (shape, M) against the full oracle product."""
     run(M, N, K, 128, algo=1)
 
 
 @pytest.mark.parametrize("wn,splits", [(1, 1), (1, 8), (2, 4), (4, 2), (8, 1), (8, 8), (2, 1), (16, 1), (16, 4)])
 def test_skinny_every_decomposition(wn, splits):
+    """The 16-warp decode kernel (17..32 tokens by default), forced onto small token counts too."""
     import quant
     lib = quant.load_library()
     try:
+        lib.w4a16_tune_decode(1, 0, 0, 0)
         lib.w4a16_tune_skinny(wn, splits)
         run(5, 256, 2048, 128, algo=1, bias=True)
         run(16, 96, 1344, 64, algo=1)
+        run(24, 256, 2048, 128, algo=1, bias=True)
     finally:
         lib.w4a16_tune_skinny(0, 0)
+        lib.w4a16_tune_decode(0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("tn", [1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 8])
+def test_gemv_every_decomposition(tn, splits):
+    """The 8-warp decode kernel over its launch shapes: out-feature tiles per CTA x cluster size x ring depth, with
+    every activation box height (1, 2, 4, 8, 16 rows), a K that is not a multiple of the 128-k unit, group sizes
+    32/64/128 and an out-feature count that leaves the last CTA partly empty."""
+    import quant
+    lib = quant.load_library()
+    ran = 0
+    try:
+        for depth in (2, 3, 0):
+            lib.w4a16_tune_decode(2, tn, splits, depth)
+            for (M, N, K, g) in [(1, 256, 2048, 128), (2, 160, 1344, 64), (3, 256, 2048, 128), (5, 256, 2048, 128),
+                                 (8, 96, 1024, 32), (12, 160, 1344, 64), (16, 256, 2048, 128)]:
+                try:
+                    run(M, N, K, g, algo=1, bias=(M % 2 == 1))
+                    ran += 1
+                except RuntimeError as e:
+                    if "algo" not in str(e):
+                        raise                                    # only "this shape cannot run with the forced decomposition"
+    finally:
+        lib.w4a16_tune_decode(0, 0, 0, 0)
+    if ran == 0:
+        pytest.skip("no test shape can run with this forced decomposition (fewer 128-k units than K slices)")
+    flag = __import__("ctypes").c_int(-1)
+    assert lib.w4a16_device_error_flag(flag) == 0 and flag.value == 0
+
+
+def test_gemv_more_than_sixteen_tokens_in_passes():
+    """Forced onto the 8-warp kernel, 17+ tokens run as passes of 16 over gridDim.z."""
+    import quant
+    lib = quant.load_library()
+    try:
+        lib.w4a16_tune_decode(2, 0, 0, 0)
+        run(17, 256, 2048, 128, algo=1, bias=True)
+        run(40, 160, 1344, 64, algo=1)
+    finally:
+        lib.w4a16_tune_decode(0, 0, 0, 0)
 
 
 def test_identity_trick_reads_back_the_dequantised_weight():
@@ -161,6 +206,36 @@ def test_tc_opt_shapes_linearity(K, N):
     assert fro <= 2e-3, fro
     err = (out[0].float() - ref).abs().max().item()
     assert err <= 1e-2 * x.abs().max().item() * (K ** 0.5) * wd.abs().max().item()
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 16384), (16384, 4096)])
+@pytest.mark.parametrize("M", [512, 8192])
+def test_tc_opt_shapes_sampled_oracle(K, N, M):
+    """The prefill sweep of the benchmark through the plan the library selects (workspace from
+    w4a16_workspace_bytes, i.e. the split-K plan where it chooses one), against the oracle on a seeded sample of
+    16 token rows x 48 out-features."""
+    import quant
+    p = packed(N, K, 128)
+    qw, zs = to_dev(p)
+    x = make_x(M, K, seed=7 + M)
+    out = quant.gemm_awq_bias(x.cuda(), qw, zs, None, N, 128, algo=0)
+    torch.cuda.synchronize()
+    check_gemm_sampled(out[0], x, p)
+    flag = __import__("ctypes").c_int(-1)
+    assert quant.load_library().w4a16_device_error_flag(flag) == 0 and flag.value == 0
+
+
+@pytest.mark.parametrize("K,N", [(4096, 11008), (11008, 4096), (4096, 4096)])
+@pytest.mark.parametrize("M", [16, 32, 1024])
+def test_llama_shapes_group64_sampled_oracle(K, N, M):
+    """LLaMA-2-7B-shaped linears at group size 64, unsharded: decode at 16 and 32 tokens, prefill at 1024."""
+    import quant
+    p = packed(N, K, 64)
+    qw, zs = to_dev(p)
+    x = make_x(M, K, seed=11 + M)
+    out = quant.gemm_awq_bias(x.cuda(), qw, zs, None, N, 64, algo=0)
+    torch.cuda.synchronize()
+    check_gemm_sampled(out[0], x, p, n_tok=16, n_out=48)
 
 
 def test_api_contract_errors():

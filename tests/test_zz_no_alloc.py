@@ -5,15 +5,16 @@ plug-ins inside a runtime that owns the device allocator, services whose memory 
 start-up.  The split-K tcgen05 GEMM normally takes its scratch (fp32 partial tiles, arrival counters)
 from a caller-provided workspace and its error word from a one-time cudaMalloc; this entry point keeps
 all of that in a device array that is part of the library image.  Checked here, through the C ABI: its
-output against the regular entry point on two calls in a row (the array is shared and keeps the previous
-call's contents), its size limit, and that its error word stays clear.  Collected last on purpose, and
-written to pass both alone in a fresh process and after every other test."""
+output against the regular entry point and against the CPU oracle on two calls in a row (the array is shared
+and keeps the previous call's contents), its size limit, and that its error word stays clear.  Collected last on
+purpose, and written to pass both alone in a fresh process and after every other test."""
 import ctypes
 
 import numpy as np
 import pytest
 import torch
 
+import oracle
 from helpers import check_gemm_tolerance, make_packed, make_x, to_dev
 
 pytestmark = pytest.mark.gpu
@@ -44,8 +45,11 @@ def test_static_scratch_entry_point_matches_regular_entry_point():
             assert _call_static(lib, x, qw, zs, bias, out[1:M + 1], M, N, K, g) == 0
             torch.cuda.synchronize()
             assert (out[0] == 555.0).all() and (out[M + 1] == 555.0).all()         # nothing written outside
-            # same tolerance as every GEMM parity test (the K split only re-associates the fp32 sum)
+            # same tolerance as every GEMM parity test (the K split only re-associates the fp32 sum): against the
+            # regular entry point and against the oracle's dequantise-then-matmul
             check_gemm_tolerance(out[1:M + 1], ref, x, p["w_deq"], K)
+            want = oracle.gemm_f16(x.cpu().unsqueeze(0), p["w_deq"], bias.cpu().unsqueeze(0)).astype(np.float32)
+            check_gemm_tolerance(out[1:M + 1], want, x, p["w_deq"], K)
             again = torch.empty(M, N, dtype=torch.float16, device="cuda")
             assert _call_static(lib, x, qw, zs, bias, again, M, N, K, g) == 0
             torch.cuda.synchronize()
