@@ -5,7 +5,8 @@
 
 Headline (`value`): the OPT-6.7B-shaped decode sweep - M in {1,4,8,16} on (K,N) in
 {(4096,4096), (4096,16384), (16384,4096)}, g=128 - as achieved HBM GB/s (algorithmic bytes /
-device time), inputs resident in HBM.  One step = ROUNDS passes over the 12 (shape, M) launches;
+device time), inputs resident in HBM.  One step = ROUNDS passes over the 12 (shape, M) launches, ordered batch size by batch size as
+decode steps run them;
 every launch of a step reads its own weight set, so no packed byte is read twice within a step and
 the bytes that pass between two uses of a set (one whole step) are several times the L2 size.  The
 step is captured in a CUDA graph; K replays are timed with CUDA events on the launching stream.
@@ -274,6 +275,7 @@ def main():
     ap.add_argument("--reduce", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how row-parallel outputs are summed - inside the decode kernel through peer memory, or by an NCCL all-reduce")
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
+    ap.add_argument("--decode-kernel", type=int, default=0, help="tuning: 0 automatic, 1 / 2 force one of the two decode kernels")
     ap.add_argument("--workload", default="decode-sweep", choices=["decode-sweep", "opt-6.7b", "llama2-7b"],
                     help="decode-sweep (default, the headline metric) or a full random-init W4A16 decoder stack: prefill + greedy decode tokens/s")
     ap.add_argument("--layers", type=int, default=0, help="override the number of decoder layers of a model workload")
@@ -320,6 +322,8 @@ def main():
             print(json.dumps(line), flush=True)
         return
 
+    if args.decode_kernel:
+        lib.w4a16_tune_decode(args.decode_kernel, 0, 0, 0)
     peaks = measured_peaks()
     stream = torch.cuda.Stream(device=dev)
     sp = stream.cuda_stream
@@ -372,8 +376,9 @@ def main():
         if reduce and exchange is None:
             dist.all_reduce(outs[(M, K, N)])
 
-    # order of a step: round by round, shape by shape, M by M - consecutive launches never share a weight set
-    calls = [(M, K, N, rd * len(DECODE_M) + mi) for rd in range(rounds) for (K, N) in DECODE_SHAPES for mi, M in enumerate(DECODE_M)]
+    # order of a step: batch size by batch size (a decode step runs all its linears at ONE batch size), round by
+    # round, shape by shape - consecutive launches never share a weight set
+    calls = [(M, K, N, rd * len(DECODE_M) + mi) for mi, M in enumerate(DECODE_M) for rd in range(rounds) for (K, N) in DECODE_SHAPES]
     step_bytes = sum(decode_bytes(M, K, N) for (M, K, N, s) in calls)
     distinct_weight_bytes = sum((K * N // 2 + (K // G) * N * 4) for (M, K, N, s) in calls) // world
     launches_per_step = len(calls)
@@ -479,7 +484,8 @@ def main():
     if world > 1:
         line["tp_check"] = tp_check(lib, dist, exchange, weights, dev, stream, world, rank, local_shape)
     if not args.small:
-        e2e = e2e_host(lib, weights, dev, stream, world, local_shape, calls[:4 * len(DECODE_SHAPES) * len(DECODE_M)])
+        e2e_calls = [(M, K, N, rd * len(DECODE_M) + mi) for mi, M in enumerate(DECODE_M) for rd in range(min(4, rounds)) for (K, N) in DECODE_SHAPES]
+        e2e = e2e_host(lib, weights, dev, stream, world, local_shape, e2e_calls)
         if rank == 0:
             line["e2e"] = e2e
         if world == 1:

@@ -130,6 +130,19 @@ int w4a16_convert_awq_to_lmdeploy(const void* qweight_src, void* qweight_dst,
                                   int in_features, int out_features, void* stream);
 
 /*
+ * Quantise and pack in one pass: fp16 weight [N, K] -> qweight int32 [K, N/8] (tile order) and zeros_scales fp16
+ * [K/g, 2N], bit-identical to the reference's flow quant_lmdeploy (test/nvidia/utils/quant_dequant_nvidia.py:5-32):
+ * quantize_tensor (:124-148, per-group asymmetric min-max in fp16, torch.round = half to even) + write_4bit_tensor
+ * (:79-88) + transpose_merge_zeros_scales + convert_ours_to_awq + convert_awq_to_lmdeploy (format.cu:206-239,
+ * 151-201, 135-149).  Optional outputs (NULL to skip): w_fp16 [N, K] = (q - zero) * scale as the quantizer returns
+ * it, zeros / scales fp16 [N, K/g] and the "ours" bytes uint8 [N, K/2] (byte = q[n,2i] << 4 | q[n,2i+1]) that
+ * generate_quant (:103-122) returns.  g in {32, 64, 128}, N % 32 == 0, K % g == 0; weight and w_fp16 8-byte aligned.
+ */
+int w4a16_quantize_pack(const void* weight, void* qweight, void* zeros_scales, void* w_fp16, void* zeros,
+                        void* scales, void* qweight_ours, int in_features, int out_features, int group_size,
+                        void* stream);
+
+/*
  * The same GEMM through HOST buffers: copies x (and nothing else) host->device, runs
  * w4a16_gemm on `stream`, copies out device->host and synchronises the stream.  The
  * packed weights stay resident on the device, as they do in the reference's WALinear

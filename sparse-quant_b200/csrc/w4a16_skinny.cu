@@ -733,7 +733,13 @@ void decode_force_kernel(int which) { g_decode_kernel = which; }
 int launch_skinny(const GemmArgs& a, cudaStream_t st)
 {
     if (a.tokens == 0) return W4A16_OK;
-    if (g_decode_kernel == 2 || (g_decode_kernel == 0 && a.tokens <= 8)) return launch_gemv(a, st);
+    // Which decode kernel: measured on B200 in CUDA graphs of dependent launches, the two-CTAs-per-SM kernel wins at
+    // 5..8 tokens on matrices of up to ~9 MB (4096 x 4096 and every tensor-parallel shard of the OPT / LLaMA
+    // shapes: 3.2-5.1 us against 4.5-5.4 us), where the launch ramp it hides is most of the call; the 16-warp
+    // single-CTA kernel below, whose main loop issues fewer instructions per tile, wins on larger matrices and at 1..4
+    // tokens.
+    const bool small = (long long)a.K * a.N <= 20ll * 1000 * 1000;
+    if (g_decode_kernel == 2 || (g_decode_kernel == 0 && a.tokens >= 5 && a.tokens <= 8 && small)) return launch_gemv(a, st);
     // with the fused exchange every rank must launch the same shape: choose it from the K all ranks agreed on
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
     if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;

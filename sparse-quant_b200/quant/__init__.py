@@ -21,7 +21,7 @@ import torch
 
 __all__ = [
     "gemm_awq_ut", "transpose_merge_zeros_scales", "convert_ours_to_awq", "convert_awq_to_lmdeploy",
-    "dequant", "gemm_awq_bias", "library_path", "load_library", "launch_count",
+    "dequant", "quantize_pack", "gemm_awq_bias", "library_path", "load_library", "launch_count",
 ]
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -60,6 +60,7 @@ C_ABI = {
     "w4a16_transpose_merge_zeros_scales": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "w4a16_convert_ours_to_awq": (_ci, [_vp, _vp, _ci, _ci, _vp]),
     "w4a16_convert_awq_to_lmdeploy": (_ci, [_vp, _vp, _ci, _ci, _vp]),
+    "w4a16_quantize_pack": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "w4a16_gemm_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_gemm_host_async": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_launch_count": (ctypes.c_ulonglong, []),
@@ -334,6 +335,32 @@ def convert_awq_to_lmdeploy(qweight, qweight_dst, in_features: int, out_features
         st = load_library().w4a16_convert_awq_to_lmdeploy(qweight.data_ptr(), qweight_dst.data_ptr(),
                                                           int(in_features), int(out_features), _stream(qweight))
     _check(st, "convert_awq_to_lmdeploy")
+
+
+def quantize_pack(weight, in_features: int, out_features: int, group_size: int, parts: bool = False):
+    """fp16 weight [N, K] (CUDA) -> (weight int32 [K, N/8] tile-ordered, zeros_scales fp16 [K/g, 2N], w_fp16 [N, K])
+    in one kernel, bit-identical to the reference's quantise-and-pack flow (see w4a16_quantize_pack in
+    include/w4a16_b200.h).  parts=True also returns (qweight_ours uint8 [N, K/2], zeros, scales fp16 [N, K/g]), the
+    intermediate tensors of the reference's generate_quant."""
+    _check_tensor(weight, "weight", dtype=torch.float16, dims=2)
+    N, K, g = int(out_features), int(in_features), int(group_size)
+    _need(tuple(weight.shape) == (N, K), "Tensor weight must have shape [out_features, in_features]")
+    dev = weight.device
+    qweight = torch.empty((K, N // 8), dtype=torch.int32, device=dev)
+    zeros_scales = torch.empty((K // g if g > 0 else 0, 2 * N), dtype=torch.float16, device=dev)
+    w_fp16 = torch.empty((N, K), dtype=torch.float16, device=dev)
+    ours = zeros = scales = None
+    if parts:
+        ours = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+        zeros = torch.empty((N, K // g), dtype=torch.float16, device=dev)
+        scales = torch.empty((N, K // g), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        st = load_library().w4a16_quantize_pack(
+            weight.data_ptr(), qweight.data_ptr(), zeros_scales.data_ptr(), w_fp16.data_ptr(),
+            zeros.data_ptr() if parts else None, scales.data_ptr() if parts else None, ours.data_ptr() if parts else None,
+            K, N, g, _stream(weight))
+    _check(st, "quantize_pack")
+    return (qweight, zeros_scales, w_fp16, ours, zeros, scales) if parts else (qweight, zeros_scales, w_fp16)
 
 
 def dequant(W, W_zeros_scales, N: int, K: int, group_size: int):

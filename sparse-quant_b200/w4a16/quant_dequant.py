@@ -1,13 +1,16 @@
 """Quantise-and-pack flow (offline, once per linear).
 
 Mirrors test/nvidia/utils/quant_dequant_nvidia.py of the reference: same function names,
-arguments and return values, so `WALinear.from_float` reads the same.  The arithmetic of
-`quantize_tensor` stays in torch fp16 ops as in the reference (it runs on whichever device
-the weight lives on); the three layout steps call the sm_100a kernels through `quant`.
+arguments and return values, so `WALinear.from_float` reads the same.  `quant_lmdeploy` runs the
+whole flow as ONE sm_100a kernel (quant.quantize_pack: min/max, scale, zero point, codes and the
+final tile order in a single pass over the weight); `quantize_tensor` / `generate_quant` keep the
+reference's torch fp16 statements for callers that want the intermediate tensors, and
+`quant_lmdeploy(..., fused=False)` runs the reference's own step sequence (torch quantizer + the
+three layout kernels) - the two routes are bit-identical (tests/test_gpu_pack.py).
 """
 import torch
 
-from quant import transpose_merge_zeros_scales, convert_ours_to_awq, convert_awq_to_lmdeploy
+from quant import transpose_merge_zeros_scales, convert_ours_to_awq, convert_awq_to_lmdeploy, quantize_pack
 
 
 def quantize_tensor(w, n_bit, q_group_size):
@@ -48,10 +51,15 @@ def generate_quant(weight_fp16, input_features, n_bit, group_size):
     return write_4bit_tensor(q).contiguous(), zeros.half().contiguous(), scales.half().contiguous(), w_fp16
 
 
-def quant_lmdeploy(weight, input_features, output_features, group_size, n_bit=4):
+def quant_lmdeploy(weight, input_features, output_features, group_size, n_bit=4, fused=True):
     """fp16 weight [N, K] on a CUDA device -> (weight int32 [K, N/8] tile-ordered,
     zeros_scales fp16 [K/g, 2N], dequantised fp16 weight [N, K]).  Reference :5-32."""
     dev = weight.device
+    if n_bit != 4:
+        raise NotImplementedError("only n_bit=4 is packed by this build")
+    if fused and weight.dtype == torch.float16 and weight.is_cuda:
+        w = weight if weight.is_contiguous() else weight.contiguous()
+        return quantize_pack(w.detach(), input_features, output_features, group_size)
     qweight, zeros, scales, w_fp16 = generate_quant(weight, input_features, n_bit, group_size)
     zeros_scales = torch.empty((input_features // group_size, output_features * 2), dtype=torch.float16, device=dev)
     transpose_merge_zeros_scales(zeros, scales, zeros_scales, input_features, output_features, group_size)
