@@ -90,6 +90,24 @@ int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, 
                   void* out, int tokens, int N, int K, int group_size,
                   void* workspace, size_t workspace_bytes, void* stream, int algo, unsigned flags);
 
+/*
+ * w4a16_gemm_ex with the epilogues the reference carries as hooks around its kernel (its test script calls them
+ * gemm_awq_residual_ut and gemm_awq_silu_dot_ut, quantization/nvidia/script/gemm_awq_test.py:63-72; the kernel side
+ * is ops::SiluActivation, kernel/gemm_s4_f16/gemm_s4_f16.cu:30-40, over weights interleaved by fuse_w1_w3_s4_k_m8,
+ * format.cu:114-120):
+ *   residual (fp16 [tokens, N] or NULL): out = (fp16(acc) + bias) + residual, both adds in fp16 - the `x + linear(h)`
+ *     of a decoder block without a launch of its own; every kernel takes it;
+ *   W4A16_FLAG_SILU_MUL: the packed matrix holds the gate and up projections of a SwiGLU block with their 32-wide
+ *     out-feature tiles alternating (tile 2j = gate tile j, tile 2j+1 = up tile j; w4a16.tp.fuse_gate_up builds it in
+ *     the packed domain); out is fp16 [tokens, N/2], out[t, j] = fp16(silu(gate[t, j])) * up[t, j] with gate and up
+ *     rounded to fp16 (+ bias) first, i.e. the roundings of act_fn(gate_proj(x)) * up_proj(x).  Decode kernels only
+ *     (tokens <= 32, N % 64 == 0, no residual); W4A16_ERR_BAD_ALGO otherwise - use w4a16_silu_mul on the plain output.
+ */
+#define W4A16_FLAG_SILU_MUL 4u
+int w4a16_gemm_fused(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                     const void* residual, void* out, int tokens, int N, int K, int group_size,
+                     void* workspace, size_t workspace_bytes, void* stream, int algo, unsigned flags);
+
 /* Scratch bytes w4a16_gemm needs for this problem (0 = none).  The reference has no
  * workspace (the WorkSpace argument of Gemm_awq_pure, gemm_quant.cu:45, is unused). */
 size_t w4a16_workspace_bytes(int tokens, int N, int K, int group_size);

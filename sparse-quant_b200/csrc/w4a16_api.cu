@@ -151,31 +151,47 @@ extern "C" size_t w4a16_workspace_bytes(int tokens, int N, int K, int group_size
     return tc_workspace_bytes(tokens, N, K, group_size);
 }
 
-extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
-                             void* out, int tokens, int N, int K, int group_size, void* workspace,
-                             size_t workspace_bytes, void* stream, int algo, unsigned flags)
+extern "C" int w4a16_gemm_fused(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                const void* residual, void* out, int tokens, int N, int K, int group_size, void* workspace,
+                                size_t workspace_bytes, void* stream, int algo, unsigned flags)
 {
     int s = validate(x, qweight, zeros_scales, out, tokens, N, K, group_size);
     if (s != W4A16_OK) return s;
     if (algo != W4A16_ALGO_AUTO && algo != W4A16_ALGO_SKINNY && algo != W4A16_ALGO_TC) return W4A16_ERR_BAD_ALGO;
-    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU)) return W4A16_ERR_BAD_ALGO;
+    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU | W4A16_FLAG_SILU_MUL)) return W4A16_ERR_BAD_ALGO;
     if (tokens == 0) return W4A16_OK;
+    if (residual && ((uintptr_t)residual & 1)) return W4A16_ERR_MISALIGNED;
     s = check_device();
     if (s != W4A16_OK) return s;
 
     GemmArgs a;
     a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
-    a.bias = (const __half*)bias; a.out = (__half*)out;
+    a.bias = (const __half*)bias; a.out = (__half*)out; a.residual = (const __half*)residual;
     a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
     a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
     a.relu = (flags & W4A16_FLAG_RELU) != 0;
+    a.silu_mul = (flags & W4A16_FLAG_SILU_MUL) != 0;
 
     if (algo == W4A16_ALGO_AUTO) algo = (tokens <= 32 || !tc_supported(tokens, N, K, group_size)) ? W4A16_ALGO_SKINNY : W4A16_ALGO_TC;
+    if (a.silu_mul) {
+        // the SwiGLU epilogue lives in the decode kernels (one pass of at most 32 tokens); larger inputs use
+        // w4a16_silu_mul on the plain output
+        if (algo != W4A16_ALGO_SKINNY || tokens > 32 || (N % 64) || residual) return W4A16_ERR_BAD_ALGO;
+    }
     if (algo == W4A16_ALGO_TC) {
         if (!tc_supported(tokens, N, K, group_size)) return W4A16_ERR_BAD_ALGO;
         return launch_tc(a, workspace, workspace_bytes, (cudaStream_t)stream);
     }
     return launch_skinny(a, (cudaStream_t)stream);
+}
+
+extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                             void* out, int tokens, int N, int K, int group_size, void* workspace,
+                             size_t workspace_bytes, void* stream, int algo, unsigned flags)
+{
+    if (flags & W4A16_FLAG_SILU_MUL) return W4A16_ERR_BAD_ALGO;      // changes the output shape: w4a16_gemm_fused only
+    return w4a16_gemm_fused(x, qweight, zeros_scales, bias, nullptr, out, tokens, N, K, group_size, workspace, workspace_bytes,
+                            stream, algo, flags);
 }
 
 extern "C" int w4a16_gemm_algo(const void* x, const void* qweight, const void* zeros_scales, const void* bias,

@@ -163,6 +163,8 @@ struct GemmArgs {
     int tokens, N, K, g;
     bool static_weights;   // W4A16_FLAG_STATIC_WEIGHTS
     bool relu = false;     // W4A16_FLAG_RELU: out = max(out, 0) after the bias add
+    bool silu_mul = false; // W4A16_FLAG_SILU_MUL: gate / up tiles alternate, out = silu(gate) * up, [tokens, N / 2] (decode kernels)
+    const __half* residual = nullptr;   // [tokens, N] added after bias / ReLU, or null
     const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
 };
 

@@ -78,6 +78,8 @@ struct GemvParams {
     int swizzled;          // the activation boxes use the 128-byte swizzle
     int x_offset, w_offset;   // byte offsets in dynamic shared memory (x_offset before rounding up to 1024)
     int relu, pdl;
+    const __half* residual;   // [tokens, N] added to the output after bias / ReLU (fp16 add), or null
+    int silu_mul;          // out-feature tiles alternate gate / up; out[t, j] = silu(gate_j) * up_j, [tokens, N / 2]
     // fused all-reduce over peer memory (world == 0: plain store of this GPU's result)
     unsigned char* peer[kExchangeMaxWorld];
     unsigned char* self;
@@ -392,10 +394,9 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
     // Rank q of the cluster finalises a slice of the (token, local out-feature) space (out-feature fastest ->
     // coalesced stores).  An output is the sum of S * wk partials - K slice w of rank q lives in the ring of warp
     // (w * tn + n_local / 32) - added in a fixed order (rank-major): deterministic.
-    const int Er = rows << nloc_shift, terms = S << wk_sh;
-    const int e_lo = div_splits(Er * crank), e_hi = div_splits(Er * (crank + 1));
-    for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
-        const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+    const int terms = S << wk_sh;
+    // sum of the S * wk partials of output (token, local out-feature)
+    auto total = [&](int tok, int nl) {
         const int off = (nl >> 5) * kRingFloats + tok * 33 + (nl & 31);
         float s = 0.f;
         if (S == 1) {
@@ -414,19 +415,51 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
                 for (int j = 0; j < 8; ++j) s += v[j];
             }
         }
-        const int n = blockIdx.x * nloc + nl;
-        if (n < p.N) {
-            if (fused) {
-                // this rank's fp32 partial goes into slot [half][rank] of EVERY rank's exchange buffer (own included)
-                const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
+        return s;
+    };
+    // fp32 sum -> fp16, + bias, ReLU: the value a plain call stores
+    auto finish = [&](float s, int n) {
+        __half h = __float2half_rn(s);
+        if (p.bias) h = __hadd(h, p.bias[n]);
+        if (p.relu) h = __hmax(h, __half());
+        return h;
+    };
+    const int Er = p.silu_mul ? rows << (nloc_shift - 1) : rows << nloc_shift;
+    const int e_lo = div_splits(Er * crank), e_hi = div_splits(Er * (crank + 1));
+    if (p.silu_mul) {
+        // SwiGLU epilogue: the out-feature tiles alternate gate, up, gate, up ..., so local out-features nl and nl + 32
+        // are a (gate, up) pair and one thread owns both: out[t, j] = fp16(silu(gate)) * up, rounded like the separate
+        // activation and product kernels it replaces (ops::SiluActivation of the reference, gemm_s4_f16.cu:30-40)
+        const int half_shift = nloc_shift - 1;
+        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+            const int tok = e >> half_shift, pl = e & ((nloc >> 1) - 1);
+            const int nl = ((pl >> 5) << 6) + (pl & 31);
+            const int n = blockIdx.x * nloc + nl;
+            if (n + 32 < p.N) {
+                const float gate = __half2float(finish(total(tok, nl), n));
+                const __half up = finish(total(tok, nl + 32), n + 32);
+                const __half act = __float2half_rn(gate / (1.f + __expf(-gate)));
+                p.out[(size_t)(tok0 + tok) * (p.N >> 1) + (blockIdx.x << half_shift) + pl] = __hmul(act, up);
+            }
+        }
+    } else {
+        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+            const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+            const float s = total(tok, nl);
+            const int n = blockIdx.x * nloc + nl;
+            if (n < p.N) {
+                if (fused) {
+                    // this rank's fp32 partial goes into slot [half][rank] of EVERY rank's exchange buffer (own included)
+                    const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
 #pragma unroll
-                for (int d = 0; d < kExchangeMaxWorld; ++d)
-                    if (d < p.world) st_slot(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx, make_uint2(__float_as_uint(s), tag));
-            } else {
-                __half h = __float2half_rn(s);
-                if (p.bias) h = __hadd(h, p.bias[n]);
-                if (p.relu) h = __hmax(h, __half());
-                p.out[(size_t)(tok0 + tok) * p.N + n] = h;
+                    for (int d = 0; d < kExchangeMaxWorld; ++d)
+                        if (d < p.world) st_slot(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx, make_uint2(__float_as_uint(s), tag));
+                } else {
+                    __half h = finish(s, n);
+                    const size_t idx = (size_t)(tok0 + tok) * p.N + n;
+                    if (p.residual) h = __hadd(h, p.residual[idx]);
+                    p.out[idx] = h;
+                }
             }
         }
     }
@@ -473,9 +506,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
 #pragma unroll
             for (int src = 1; src < kExchangeMaxWorld; ++src)
                 if (src < p.world) s += __uint_as_float(v[src].x);
-            __half h = __float2half_rn(s);
-            if (p.bias) h = __hadd(h, p.bias[n]);
-            if (p.relu) h = __hmax(h, __half());
+            __half h = finish(s, n);
+            if (p.residual) h = __hadd(h, p.residual[idx]);
             p.out[idx] = h;
         }
         __syncthreads();
@@ -579,7 +611,7 @@ int max_clusters(int g, int sp, int smem)
 // Decomposition: tn out-feature tiles per CTA (16 / tn K slices), S CTAs per cluster along K.  Among the shapes that
 // run as one wave of at most one CTA per SM, pick the one with the least work on the busiest warp; clusters pay a
 // little for their two barriers and the remote loads of the reduction.
-bool pick_config(Config& best, int tokens, int N, int K, int g)
+bool pick_config(Config& best, int tokens, int N, int K, int g, int min_tn = 1)
 {
     const int sms = sm_count();
     const int n_tiles = N / kTileN, units = (K + kUnitK - 1) / kUnitK;
@@ -588,7 +620,7 @@ bool pick_config(Config& best, int tokens, int N, int K, int g)
     c0.rp = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
     c0.swizzled = c0.rp >= 4;
     double best_cost = -1.0;
-    for (int tn = 1; tn <= kWarps; tn <<= 1) {
+    for (int tn = min_tn; tn <= kWarps; tn <<= 1) {
         if (g_force_tn && tn != g_force_tn) continue;
         const int wk = kWarps / tn;
         for (int sp = 1; sp <= 8; ++sp) {
@@ -669,7 +701,8 @@ int launch_gemv(const GemmArgs& a, cudaStream_t st)
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
     if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;
     Config c;
-    if (!pick_config(c, a.tokens, a.N, k_config, a.g)) return g_force_tn || g_force_splits ? W4A16_ERR_BAD_ALGO : W4A16_ERR_BAD_SHAPE;
+    if (a.silu_mul && ((a.N % 64) || a.exchange || a.residual)) return W4A16_ERR_BAD_SHAPE;
+    if (!pick_config(c, a.tokens, a.N, k_config, a.g, a.silu_mul ? 2 : 1)) return g_force_tn || g_force_splits ? W4A16_ERR_BAD_ALGO : W4A16_ERR_BAD_SHAPE;
 
     GemvParams p;
     p.zs = a.zs; p.bias = a.bias; p.out = a.out;
@@ -696,6 +729,7 @@ int launch_gemv(const GemmArgs& a, cudaStream_t st)
     p.depth = c.depth; p.ahead = c.ahead; p.rp = c.rp; p.swizzled = c.swizzled;
     p.x_offset = c.x_offset; p.w_offset = c.w_offset;
     p.relu = a.relu ? 1 : 0; p.pdl = a.static_weights ? 1 : 0;
+    p.residual = a.residual; p.silu_mul = a.silu_mul ? 1 : 0;
     p.timeline = g_timeline;
 
     const int n_tiles = a.N / kTileN;

@@ -82,6 +82,8 @@ struct SkinnyParams {
     int ring_offset; // byte offset of the per-warp rings in shared memory
     int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
+    const __half* residual;   // [tokens, N] added to the output after bias / ReLU (fp16 add), or null
+    int silu_mul;    // out-feature tiles alternate gate / up; out[t, j] = silu(gate_j) * up_j, [tokens, N / 2]
     int relu;        // clamp the outputs at zero after the bias add
     int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
     // fused all-reduce over peer memory (world == 0: plain store of this GPU's result)
@@ -449,10 +451,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     // Rank r finalises a slice of the (tok, n_local) space (n fastest -> coalesced stores).  An output is
     // the sum of S * wk partials - K slice w of rank q lives in the ring of warp (w * wn + n_local / 32) -
     // added in a fixed order (rank-major) from batches of eight loads in flight: deterministic.
-    const int Er = rows << nloc_shift, terms = S << wk_shift;
-    const int e_lo = div_splits(Er * rank), e_hi = div_splits(Er * (rank + 1));
-    for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
-        const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+    const int terms = S << wk_shift;
+    // sum of the S * wk partials of output (token, local out-feature)
+    auto total = [&](int tok, int nl) {
         const int off = (nl >> 5) * kRingFloats + tok * 33 + (nl & 31);
         float s = 0.f;
         for (int t0 = 0; t0 < terms; t0 += 8) {
@@ -465,19 +466,52 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
 #pragma unroll
             for (int j = 0; j < 8; ++j) s += v[j];
         }
-        const int n = blockIdx.x * nloc + nl;
-        if (n < p.N) {
-            if (fused) {
-                // this rank's fp32 partial goes into slot [half][rank] of EVERY rank's exchange buffer (own included)
-                const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
+        return s;
+    };
+    // fp32 sum -> fp16, + bias, ReLU: the value a plain call stores
+    auto finish = [&](float s, int n) {
+        __half h = __float2half_rn(s);
+        if (p.bias) h = __hadd(h, p.bias[n]);
+        if (p.relu) h = __hmax(h, __half());
+        return h;
+    };
+    const int Er = p.silu_mul ? rows << (nloc_shift - 1) : rows << nloc_shift;
+    const int e_lo = div_splits(Er * rank), e_hi = div_splits(Er * (rank + 1));
+    if (p.silu_mul) {
+        // SwiGLU epilogue: the out-feature tiles alternate gate, up, gate, up ... (fused that way at load time), so
+        // local out-features nl and nl + 32 are a (gate, up) pair of the same hidden unit and one thread owns both:
+        // out[t, j] = fp16(silu(gate)) * up, rounded like the separate activation and product kernels it replaces
+        // (the reference carries the same epilogue as ops::SiluActivation, gemm_s4_f16.cu:30-40).
+        const int half_shift = nloc_shift - 1;
+        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+            const int tok = e >> half_shift, pl = e & ((nloc >> 1) - 1);
+            const int nl = ((pl >> 5) << 6) + (pl & 31);
+            const int n = blockIdx.x * nloc + nl;
+            if (n + 32 < p.N) {
+                const float gate = __half2float(finish(total(tok, nl), n));
+                const __half up = finish(total(tok, nl + 32), n + 32);
+                const __half act = __float2half_rn(gate / (1.f + __expf(-gate)));
+                p.out[(size_t)(tok0 + tok) * (p.N >> 1) + (blockIdx.x << half_shift) + pl] = __hmul(act, up);
+            }
+        }
+    } else {
+        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
+            const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+            const float s = total(tok, nl);
+            const int n = blockIdx.x * nloc + nl;
+            if (n < p.N) {
+                if (fused) {
+                    // this rank's fp32 partial goes into slot [half][rank] of EVERY rank's exchange buffer (own included)
+                    const size_t idx = (size_t)(half_sel * p.world + p.rank) * p.capacity + (size_t)(tok0 + tok) * p.N + n;
 #pragma unroll
-                for (int d = 0; d < kExchangeMaxWorld; ++d)
-                    if (d < p.world) st_slot(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx, make_uint2(__float_as_uint(s), tag));
-            } else {
-                __half h = __float2half_rn(s);
-                if (p.bias) h = __hadd(h, p.bias[n]);
-                if (p.relu) h = __hmax(h, __half());
-                p.out[(size_t)(tok0 + tok) * p.N + n] = h;
+                    for (int d = 0; d < kExchangeMaxWorld; ++d)
+                        if (d < p.world) st_slot(reinterpret_cast<uint2*>(p.peer[d] + kExchangeDataOffset) + idx, make_uint2(__float_as_uint(s), tag));
+                } else {
+                    __half h = finish(s, n);
+                    const size_t idx = (size_t)(tok0 + tok) * p.N + n;
+                    if (p.residual) h = __hadd(h, p.residual[idx]);
+                    p.out[idx] = h;
+                }
             }
         }
     }
@@ -525,9 +559,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
 #pragma unroll
             for (int src = 1; src < kExchangeMaxWorld; ++src)
                 if (src < p.world) s += __uint_as_float(v[src].x);
-            __half h = __float2half_rn(s);
-            if (p.bias) h = __hadd(h, p.bias[n]);
-            if (p.relu) h = __hmax(h, __half());
+            __half h = finish(s, n);
+            if (p.residual) h = __hadd(h, p.residual[idx]);
             p.out[idx] = h;
         }
         __syncthreads();
@@ -546,7 +579,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
 
 struct Config { int tg, wn, splits, depth, warps; };
 
-int g_force_wn = 0, g_force_splits = 0, g_force_depth = 0, g_force_warps = 0, g_debug_mode = 0;
+int g_force_wn = 0, g_force_splits = 0, g_force_depth = 0, g_debug_mode = 0;
 unsigned long long* g_timeline = nullptr;
 
 constexpr int kSmemBudget = 227 * 1024;                  // opt-in shared memory of one CTA on sm_100
@@ -616,7 +649,7 @@ int max_clusters(int tg, int g, int sp)
     }
 }
 
-Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
+Config pick_config(int tokens, int N, int K, int g, int max_tg = 4, int min_wn = 1)
 {
     Config c;
     c.tg = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
@@ -635,7 +668,7 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
     if (c.depth > max_depth_for(c.tg)) c.depth = max_depth_for(c.tg);
     if (g_force_depth && g_force_depth < c.depth) c.depth = g_force_depth;
     // out-feature tiles per CTA: about one CTA per SM in a single wave
-    c.wn = 1;
+    c.wn = min_wn;
     while (c.wn < kWarps && (long long)((n_tiles + c.wn - 1) / c.wn) * c.splits > 148) c.wn <<= 1;
     // every K slice of a CTA should own at least one 128-k unit
     while (c.wn < kWarps && (kWarps / c.wn) * c.splits > units) c.wn <<= 1;
@@ -645,7 +678,7 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4)
         // of the SMs idle (e.g. 384 out-feature tiles: 48 x 2 CTAs).  Search all (tiles per CTA, cluster size <= 8)
         // for the most CTAs within one wave, weighted by how deep a ring still fits; ties go to the smaller cluster.
         double best = -1.0;
-        for (int wn = 1; wn <= kWarps; wn <<= 1) {
+        for (int wn = min_wn; wn <= kWarps; wn <<= 1) {
             for (int sp = 1; sp <= 8; ++sp) {
                 if (sp > units) break;
                 const long long ctas = (long long)((n_tiles + wn - 1) / wn) * sp;
@@ -720,14 +753,13 @@ void skinny_set_timeline(unsigned long long* buf) { g_timeline = buf; }
 
 void skinny_force_config(int wn, int splits)
 {
-    g_force_wn = wn & 0xff;
-    g_debug_mode = (wn >> 8) & 0xff;
-    g_force_splits = splits & 0xff;
-    g_force_depth = (splits >> 8) & 0xff;
-    g_force_warps = (splits >> 16) & 0xff;
+    g_force_wn = wn < 0 ? 0 : wn;
+    g_force_splits = splits < 0 ? 0 : splits;
 }
+// debug builds: experiment switches of the kernel (bit 0 no MMAs, bit 1 no activation staging) and a ring-depth cap
+void skinny_debug_mode(int mode, int depth) { g_debug_mode = mode; g_force_depth = depth; }
 
-int g_decode_kernel = 0;      // 0: by token count, 1: always the 16-warp kernel, 2: always the 8-warp kernel
+int g_decode_kernel = 0;      // 0: by measured crossover, 1: always the 16-warp kernel, 2: always the two-CTAs-per-SM kernel
 void decode_force_kernel(int which) { g_decode_kernel = which; }
 
 int launch_skinny(const GemmArgs& a, cudaStream_t st)
@@ -743,18 +775,20 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     // with the fused exchange every rank must launch the same shape: choose it from the K all ranks agreed on
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
     if (k_config < a.K) return W4A16_ERR_BAD_SHAPE;
-    Config c = pick_config(a.tokens, a.N, k_config, a.g);
+    const int min_wn = a.silu_mul ? 2 : 1;                 // a (gate, up) pair of tiles stays inside one CTA
+    if (a.silu_mul && ((a.N % 64) || a.exchange || a.residual)) return W4A16_ERR_BAD_SHAPE;
+    Config c = pick_config(a.tokens, a.N, k_config, a.g, 4, min_wn);
     // 17..32 tokens with a K so long that the staged activations need clusters of 8 CTAs: such clusters do not
     // always fit the machine in one wave; two passes of 16 tokens (gridDim.z, the second one reading the weights
     // from L2) are faster.  Not with the fused exchange, which needs all tokens in one pass.
-    if (c.tg == 4 && c.splits >= 8 && !a.exchange && !g_force_splits) c = pick_config(a.tokens, a.N, k_config, a.g, 2);
+    if (c.tg == 4 && c.splits >= 8 && !a.exchange && !g_force_splits) c = pick_config(a.tokens, a.N, k_config, a.g, 2, min_wn);
     if (c.depth < 2) return W4A16_ERR_BAD_SHAPE;         // forced configuration does not fit in shared memory
     const int kUnitK = unit_k_for(c.tg), kUnitTiles = kUnitK / kTileK;
     const int units = (a.K + kUnitK - 1) / kUnitK;
     if (c.splits > (k_config + kUnitK - 1) / kUnitK) c.splits = 1;
     const int kWarps = c.warps;
     if (c.wn != 1 && c.wn != 2 && c.wn != 4 && c.wn != 8 && c.wn != 16 && c.wn != 32) return W4A16_ERR_BAD_ALGO;
-    if (c.wn > kWarps) return W4A16_ERR_BAD_ALGO;
+    if (c.wn > kWarps || c.wn < min_wn) return W4A16_ERR_BAD_ALGO;
     if (c.splits < 1 || c.splits > 8) return W4A16_ERR_BAD_ALGO;
 
     SkinnyParams p;
@@ -778,6 +812,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     while ((1 << p.wn_shift) < c.wn) ++p.wn_shift;
     p.inv_splits = c.splits > 1 ? (unsigned)(((1ull << 32) + c.splits - 1) / c.splits) : 0u;
     p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0; p.relu = a.relu ? 1 : 0;
+    p.residual = a.residual; p.silu_mul = a.silu_mul ? 1 : 0;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
     const int tok = 8 * c.tg;

@@ -77,6 +77,7 @@ struct TcParams {
     int tokens, N, K, g;
     int n_blocks, t_blocks;
     int relu;                       // clamp the outputs at zero after the bias add
+    const __half* residual;         // [tokens, N] added after bias / ReLU (fp16 add), or null
     int split;                      // K parts per output tile (1 = no split)
     float* partial;                 // split > 1: fp32 partial tiles [split][tokens][N]
     int*   counters;                // split > 1: arrivals per output tile (zero on entry, reset by the last arriver)
@@ -291,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                                 __half h = __float2half_rn(__uint_as_float(v[j]));
                                 if (p.bias) h = __hadd(h, bias);
                                 if (p.relu) h = __hmax(h, __half());
+                                if (p.residual) h = __hadd(h, p.residual[(size_t)t * p.N + n]);
                                 p.out[(size_t)t * p.N + n] = h;
                             }
                         }
@@ -342,6 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                                     __half h = __float2half_rn(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j]);
                                     if (p.bias) h = __hadd(h, bias);
                                     if (p.relu) h = __hmax(h, __half());
+                                    if (p.residual) h = __hadd(h, p.residual[(size_t)t * p.N + n]);
                                     p.out[(size_t)t * p.N + n] = h;
                                 }
                             }
@@ -495,7 +498,7 @@ int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaSt
 
     TcParams p;
     p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out; p.error = err;
-    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.g = a.g; p.relu = a.relu ? 1 : 0;
+    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.g = a.g; p.relu = a.relu ? 1 : 0; p.residual = a.residual;
     p.n_blocks = (a.N + kBlockN - 1) / kBlockN;
     p.t_blocks = (a.tokens + tok - 1) / tok;
     const long long tiles = (long long)p.n_blocks * p.t_blocks;

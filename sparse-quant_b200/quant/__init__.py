@@ -38,6 +38,7 @@ C_ABI = {
     "w4a16_gemm": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp]),
     "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
     "w4a16_gemm_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
+    "w4a16_gemm_fused": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
     "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
     "w4a16_exchange_bytes": (_sz, [_ci, _sz]),
     "w4a16_exchange_alloc": (_ci, [_ci, _sz, ctypes.POINTER(_vp)]),
@@ -135,10 +136,11 @@ def launch_count() -> int:
 
 FLAG_STATIC_WEIGHTS = 1
 FLAG_RELU = 2
+FLAG_SILU_MUL = 4
 
 
 def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None,
-                  static_weights: bool = False, relu: bool = False):
+                  static_weights: bool = False, relu: bool = False, residual=None, silu_mul: bool = False):
     """gemm_awq_ut with the fp16 bias add of WALinear.forward fused into the kernel epilogue.
 
     I fp16 [b, s, K] (CUDA, contiguous); W int32 [K, N/8] tile-ordered; W_zeros_scales fp16
@@ -146,6 +148,8 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
     static_weights=True passes W4A16_FLAG_STATIC_WEIGHTS (see include/w4a16_b200.h): only for weights
     that were written before anything still in flight on the current stream was enqueued.
     relu=True passes W4A16_FLAG_RELU: max(., 0) applied after the bias add.
+    residual (fp16 [b, s, N]) is added to the output in the kernel epilogue; silu_mul=True passes
+    W4A16_FLAG_SILU_MUL (gate / up tiles interleaved, see w4a16_gemm_fused): returns fp16 [b, s, N/2].
     """
     _check_tensor(I, "I", dtype=torch.float16, dims=3)
     _check_tensor(W, "W", dims=2)
@@ -161,21 +165,27 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
     if bias is not None:
         _check_tensor(bias, "bias", dtype=torch.float16)
         _need(bias.numel() == N and bias.device == I.device, "Tensor bias must have N elements on the same device")
+    n_out = N // 2 if silu_mul else N
+    if residual is not None:
+        _check_tensor(residual, "residual", dtype=torch.float16)
+        _need(residual.numel() == b * s * N and residual.device == I.device, "Tensor residual must have b*s*N elements")
     if out is None:
-        out = torch.empty((b, s, N), dtype=torch.float16, device=I.device)
+        out = torch.empty((b, s, n_out), dtype=torch.float16, device=I.device)
     else:
         _check_tensor(out, "O", dtype=torch.float16, dims=3)
-        _need(tuple(out.shape) == (b, s, N) and out.device == I.device, "Tensor O must have shape [b, s, N]")
+        _need(tuple(out.shape) == (b, s, n_out) and out.device == I.device, "Tensor O must have shape [b, s, N]")
     lib = load_library()
     tokens = b * s
     with torch.cuda.device(I.device):
         ws_bytes = lib.w4a16_workspace_bytes(tokens, N, K, group_size)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=I.device) if ws_bytes else None
-        st = lib.w4a16_gemm_ex(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
-                               bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                               tokens, N, K, group_size,
-                               ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo),
-                               (FLAG_STATIC_WEIGHTS if static_weights else 0) | (FLAG_RELU if relu else 0))
+        st = lib.w4a16_gemm_fused(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                  bias.data_ptr() if bias is not None else None,
+                                  residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                  tokens, N, K, group_size,
+                                  ws.data_ptr() if ws is not None else None, ws_bytes, _stream(I), int(algo),
+                                  (FLAG_STATIC_WEIGHTS if static_weights else 0) | (FLAG_RELU if relu else 0) |
+                                  (FLAG_SILU_MUL if silu_mul else 0))
     _check(st, "gemm_awq_ut")
     return out
 

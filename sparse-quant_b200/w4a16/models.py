@@ -28,7 +28,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .qlinear import WALinear
-from .tp import ColumnParallelWALinear, RowParallelWALinear, fuse_columns, shard_ranges
+from .tp import ColumnParallelWALinear, RowParallelWALinear, fuse_columns, fuse_gate_up, shard_ranges, split_gate_up
 
 
 @dataclass
@@ -129,7 +129,8 @@ class DecoderLayer(nn.Module):
             self.ln2 = source.norm(idx, "ln2", nn.LayerNorm(H, device=device, dtype=torch.float16))
             self.fc2 = RowParallelWALinear(source.linear(idx, "fc2", cfg.ffn, H), rank, world, group, ranges=ffn_ranges, exchange=exchange)
         else:
-            self.gate_up_proj = fuse_columns([col("gate_proj", cfg.ffn, ffn_ranges), col("up_proj", cfg.ffn, ffn_ranges)])
+            # gate and up tiles alternate, so that the decode kernel applies silu(gate) * up in its epilogue
+            self.gate_up_proj = fuse_gate_up(col("gate_proj", cfg.ffn, ffn_ranges), col("up_proj", cfg.ffn, ffn_ranges))
             self.ln1 = source.norm(idx, "ln1", RMSNorm(H, cfg.rms_eps, device))
             self.ln2 = source.norm(idx, "ln2", RMSNorm(H, cfg.rms_eps, device))
             self.fc2 = RowParallelWALinear(source.linear(idx, "down_proj", cfg.ffn, H), rank, world, group, ranges=ffn_ranges, exchange=exchange)
@@ -162,7 +163,7 @@ class DecoderLayer(nn.Module):
             f = torch.relu(self.fc1(h.reshape(1, B * S, H)))           # the reference's FFN sees [1, B*S, H] (:599-606)
             x = x + self.fc2(f).reshape(B, S, H)
         else:
-            gate, up = self.gate_up_proj(h).chunk(2, dim=-1)
+            gate, up = split_gate_up(self.gate_up_proj(h))
             x = x + self.fc2(F.silu(gate) * up)
         return x
 
@@ -189,7 +190,11 @@ def _layer_forward_static(self, x, delta, pos_t, rope):
     if self.cfg.kind == "opt":
         delta = self.fc2(self.fc1(h.reshape(1, B, H), relu=True)).reshape(B, 1, H)
     else:
-        delta = self.fc2(silu_mul(self.gate_up_proj(h)))
+        if B <= 32:
+            delta = self.fc2(self.gate_up_proj(h, silu_mul=True))           # SwiGLU product in the GEMV epilogue
+        else:
+            gate, up = split_gate_up(self.gate_up_proj(h))
+            delta = self.fc2(silu_mul(torch.cat((gate, up), dim=-1)))
     return x, delta
 
 

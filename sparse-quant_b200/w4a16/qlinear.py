@@ -40,18 +40,26 @@ class WALinear(nn.Module):
             self.register_buffer("bias", None)
 
     @torch.no_grad()
-    def forward(self, x, relu: bool = False):
+    def forward(self, x, relu: bool = False, residual=None, silu_mul: bool = False):
         """x fp16 [..., K] -> fp16 [..., N].  The reference requires 3-D input (gemm_quant.cu:73);
-        2-D and >3-D inputs are viewed as [1, tokens, K] here.  relu=True fuses the ReLU that follows (OPT's fc1)
-        into the kernel epilogue."""
+        2-D and >3-D inputs are viewed as [1, tokens, K] here.  Epilogues fused into the kernel: relu=True (the
+        ReLU after OPT's fc1), residual (fp16 [..., N], added to the output), silu_mul=True (a fuse_gate_up linear
+        at up to 32 tokens: returns silu(gate) * up, [..., N / 2])."""
         shape = x.shape
         x3 = x if x.dim() == 3 else x.reshape(1, -1, shape[-1])
         if not x3.is_contiguous():
             x3 = x3.contiguous()
-        extra = {"relu": True} if relu else {}
+        extra = {}
+        if relu:
+            extra["relu"] = True
+        if silu_mul:
+            extra["silu_mul"] = True
+        if residual is not None:
+            extra["residual"] = residual if residual.is_contiguous() else residual.contiguous()
         y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size,
                           static_weights=self.static_weights, **extra)
-        return y if x.dim() == 3 else y.reshape(*shape[:-1], self.out_features)
+        n_out = self.out_features // 2 if silu_mul else self.out_features
+        return y if x.dim() == 3 else y.reshape(*shape[:-1], n_out)
 
     @staticmethod
     def from_float(module, w_config, a_config=None, quantize_output=False):

@@ -95,6 +95,38 @@ def fuse_columns(linears):
     return fused
 
 
+def fuse_gate_up(gate, up):
+    """The gate and up projections of a SwiGLU block -> ONE WALinear whose 32-wide out-feature tiles alternate
+    gate, up, gate, up ...: tile 2j of the fused matrix is tile j of `gate`, tile 2j + 1 is tile j of `up`.  With that
+    order a (gate, up) pair of the same hidden unit sits 32 columns apart inside one CTA of the decode kernels, which
+    can then apply silu(gate) * up in their epilogue (W4A16_FLAG_SILU_MUL, include/w4a16_b200.h) - what the
+    reference's fuse_w1_w3_s4_k_m8 (kernel/gemm_s4_f16/format.cu:114-120) prepares for its ops::SiluActivation.
+    Built in the packed domain without re-quantising, like fuse_columns.  `split_gate_up` undoes the order on a
+    plain output."""
+    a, b = [l.linear if isinstance(l, ColumnParallelWALinear) else l for l in (gate, up)]
+    K, g, n = a.in_features, a.group_size, a.out_features
+    assert b.in_features == K and b.group_size == g and b.out_features == n, "gate and up must have the same shape"
+    assert (a.bias is None) == (b.bias is None)
+    t = n // 32
+    w = torch.stack([a.weight.reshape(K // 32, t, 128), b.weight.reshape(K // 32, t, 128)], dim=2)     # [K/32][t][2][128]
+    w = w.reshape(K, 2 * n // 8).contiguous()
+    zs = torch.stack([a.zeros_scales.reshape(K // g, t, 64), b.zeros_scales.reshape(K // g, t, 64)], dim=2)
+    zs = zs.reshape(K // g, 4 * n).contiguous()
+    bias = None
+    if a.bias is not None:
+        bias = torch.stack([a.bias.reshape(t, 32), b.bias.reshape(t, 32)], dim=1).reshape(1, 2 * n).contiguous()
+    fused = _from_buffers(w, zs, bias, g)
+    fused.static_weights = a.static_weights and b.static_weights
+    return fused
+
+
+def split_gate_up(y):
+    """[..., 2n] output of a fuse_gate_up linear -> (gate [..., n], up [..., n])."""
+    n2 = y.shape[-1]
+    v = y.reshape(*y.shape[:-1], n2 // 64, 2, 32)
+    return v[..., 0, :].reshape(*y.shape[:-1], n2 // 2), v[..., 1, :].reshape(*y.shape[:-1], n2 // 2)
+
+
 class ColumnParallelWALinear(nn.Module):
     """y_local = x @ W[n0:n1]^T (+ b[n0:n1]); the output stays sharded (feeds attention heads or the
     elementwise activation of the FFN)."""

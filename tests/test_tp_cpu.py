@@ -157,3 +157,25 @@ def test_fused_sibling_linears_are_the_concatenation_of_their_dequantised_weight
     assert torch.equal(fused.bias, torch.cat([p.bias for p in parts], dim=1))
     with pytest.raises(AssertionError):
         fuse_columns([parts[0], _packed_linear(32, 128, g, seed=1)])          # different K
+
+
+def test_gate_up_fusion_alternates_tiles_of_32_out_features():
+    """fuse_gate_up interleaves gate and up at tile granularity in the packed domain: rows 64j..64j+31 of the
+    dequantised fused matrix are rows 32j..32j+31 of gate, the next 32 those of up; split_gate_up undoes it."""
+    from w4a16.tp import fuse_gate_up, split_gate_up
+    K, g, n = 256, 64, 96
+    gate, up = _packed_linear(n, K, g, seed=31), _packed_linear(n, K, g, seed=32)
+    fused = fuse_gate_up(gate, up)
+    assert fused.out_features == 2 * n and fused.in_features == K
+
+    def deq(p):
+        return oracle.dequant(p.weight.numpy().view(np.uint32), p.zeros_scales.numpy().view(np.uint16), K, p.out_features, g)
+    got = deq(fused).reshape(n // 32, 2, 32, K)
+    assert np.array_equal(got[:, 0].reshape(n, K).view(np.uint16), deq(gate).view(np.uint16))
+    assert np.array_equal(got[:, 1].reshape(n, K).view(np.uint16), deq(up).view(np.uint16))
+    b = fused.bias.reshape(n // 32, 2, 32)
+    assert torch.equal(b[:, 0].reshape(1, n), gate.bias) and torch.equal(b[:, 1].reshape(1, n), up.bias)
+    y = torch.arange(2 * 2 * n, dtype=torch.float32).reshape(2, 2 * n)
+    a, c = split_gate_up(y)
+    assert torch.equal(a, y.reshape(2, n // 32, 2, 32)[:, :, 0].reshape(2, n))
+    assert torch.equal(c, y.reshape(2, n // 32, 2, 32)[:, :, 1].reshape(2, n))
