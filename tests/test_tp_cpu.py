@@ -34,11 +34,12 @@ def _packed_linear(N, K, g, seed, bias=True):
     return lin
 
 
-def _oracle_forward(I, W, ZS, bias, N, g, algo=0, out=None, static_weights=False):
+def _oracle_forward(I, W, ZS, bias, N, g, algo=0, out=None, static_weights=False, relu=False):
     """Stand-in for quant.gemm_awq_bias on CPU tensors (same signature)."""
     b, s, K = I.shape
     y = oracle.gemm_awq(I.reshape(-1, K), W.numpy(), ZS.numpy(), N, K, g, None if bias is None else bias.reshape(-1))
-    return torch.from_numpy(y.copy()).reshape(b, s, N)
+    y = torch.from_numpy(y.copy()).reshape(b, s, N)
+    return torch.relu(y) if relu else y
 
 
 def test_shard_ranges_even_and_uneven():
