@@ -5,9 +5,8 @@
 
 Headline (`value`): the OPT-6.7B-shaped decode sweep - M in {1,4,8,16} on (K,N) in
 {(4096,4096), (4096,16384), (16384,4096)}, g=128 - as achieved HBM GB/s (algorithmic bytes /
-device time), inputs resident in HBM.  One step = ROUNDS passes over the 12 (shape, M) launches, ordered batch size by batch size as
-decode steps run them;
-every launch of a step reads its own weight set, so no packed byte is read twice within a step and
+device time), inputs resident in HBM.  One step = ROUNDS passes over the 12 (shape, M) launches,
+ordered batch size by batch size as decode steps run them; every launch of a step reads its own weight set, so no packed byte is read twice within a step and
 the bytes that pass between two uses of a set (one whole step) are several times the L2 size.  The
 step is captured in a CUDA graph; K replays are timed with CUDA events on the launching stream.
 Extra keys: `e2e` (same sweep through the host-buffer C-ABI call), `roofline`, `cpu_baseline`,
@@ -48,10 +47,10 @@ DECODE_M = [1, 4, 8, 16]
 PREFILL_M = [512, 2048, 8192]
 ROUNDS = 32                                                      # passes over the 12 (shape, M) launches per step
 WORKLOAD = "OPT-6.7B decode GEMV sweep: M in {1,4,8,16} x (K,N) in {4096x4096, 4096x16384, 16384x4096}, g=128"
-# DRAM bytes moved per algorithmic byte, from an ncu capture of 12 consecutive launches of the step
-# (profiles/gemv_kernel_step_order_dram_bytes.md: dram__bytes_read.sum + dram__bytes_write.sum over the launches
-# divided by their algorithmic bytes)
-TRAFFIC_RATIO = 1.0004
+# DRAM bytes moved per algorithmic byte, from an ncu capture of the 12 launches of one round in the step's order
+# (profiles/decode_sweep_step_order_launches.md: dram__bytes_read.sum + dram__bytes_write.sum over the launches
+# divided by their algorithmic bytes; a little below one because activations and outputs stay in L2)
+TRAFFIC_RATIO = 0.9974
 
 
 def decode_bytes(M, K, N, g=G, bias=False):
@@ -475,8 +474,8 @@ def main():
     alg = step_bytes / launches_per_step / world
     line["roofline"] = {
         "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": per_gpu / peaks["hbm_gbs"],
-        "traffic": TRAFFIC_RATIO * alg, "traffic_source": "profiles/gemv_kernel_step_order_dram_bytes.md (ncu, 12 consecutive launches in the step's order)",
-        "kernel": "gemv_kernel", "peak_source": f"of {peaks['source']} (copy bandwidth)",
+        "traffic": TRAFFIC_RATIO * alg, "traffic_source": "profiles/decode_sweep_step_order_launches.md (ncu, the 12 launches of one round in the step's order)",
+        "kernel": "skinny_kernel (gemv_kernel for 5..8 tokens on matrices up to ~9 MB)", "peak_source": f"of {peaks['source']} (copy bandwidth)",
         "algorithmic_bytes_per_launch": alg,
         "avg_launch_us": 1e3 * ms / (args.steps * launches_per_step),
     }
