@@ -137,32 +137,48 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
+        // Three lanes share the copies of a stage, so that the address arithmetic and issue latency of one thread is
+        // not what paces the pipeline: lane 0 arms the barrier and fetches the activation tile, lane 1 the two rows of
+        // packed tiles, lane 2 the group's (zero, scale) row.  Copies that complete before lane 0 has armed the
+        // barrier only drive its byte count negative for a moment; the phase cannot complete before lane 0's arrival.
+        if (lane < 3) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            const uint32_t row_words = (uint32_t)n_tiles * 32u;                 // uint4 per k-tile row of the packed matrix
+            const int steps_per_group = p.g / kBlockK;                          // 1 or 2 (g = 64 or 128)
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const int tile = item / p.split;
                 const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
                 const int nb_tiles = min(4, n_tiles - nb * 4);
                 int ks0, ks1;
                 k_range(item, ks0, ks1);
+                const uint32_t w_bytes = nb_tiles * 512u, zs_bytes = nb_tiles * 128u;
+                const uint32_t tx = Cfg::kXBytes + 2 * w_bytes + zs_bytes;
+                const uint4* wsrc = p.qw + (size_t)(ks0 * 2) * row_words + nb * 4 * 32;
+                int kg = (ks0 * kBlockK) / p.g, in_group = ks0 % steps_per_group;
+                const uint32_t* zsrc = p.zs + (size_t)kg * p.N + nb * kBlockN;
+                int kcoord = ks0 * kBlockK;
                 for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
                     const uint32_t st = smem_base + stage * Cfg::kStageBytes;
-                    const uint32_t w_bytes = nb_tiles * 512u, zs_bytes = nb_tiles * 128u;
-                    mbar_arrive_expect_tx(full_bar(stage), Cfg::kXBytes + 2 * w_bytes + zs_bytes);
-                    tma_load_2d(st, &x_map, ks * kBlockK, tb * TOK, full_bar(stage));
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        bulk_load(st + Cfg::kXBytes + j * 2048, p.qw + ((size_t)(ks * 2 + j) * n_tiles + nb * 4) * 32,
-                                  w_bytes, full_bar(stage));
-                    const int kg = (ks * kBlockK) / p.g;
-                    bulk_load(st + Cfg::kXBytes + Cfg::kWBytes, p.zs + (size_t)kg * p.N + nb * kBlockN, zs_bytes, full_bar(stage));
+                    const uint32_t bar = full_bar(stage);
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(bar, tx);
+                        tma_load_2d(st, &x_map, kcoord, tb * TOK, bar);
+                    } else if (lane == 1) {
+                        bulk_load(st + Cfg::kXBytes, wsrc, w_bytes, bar);
+                        bulk_load(st + Cfg::kXBytes + 2048, wsrc + row_words, w_bytes, bar);
+                    } else {
+                        bulk_load(st + Cfg::kXBytes + Cfg::kWBytes, zsrc, zs_bytes, bar);
+                    }
+                    wsrc += 2 * row_words;
+                    kcoord += kBlockK;
+                    if (++in_group == steps_per_group) { in_group = 0; zsrc += p.N; }
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // give copies already in flight time to land before the CTA releases its shared memory
                 const uint64_t t0 = globaltimer_ns();
                 while (globaltimer_ns() - t0 < 200000) { }
@@ -172,6 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16_m128(TOK);
+            const uint64_t bdesc0 = smem_desc_sw128(smem_base);        // stage s: the start-address field advances by s * kStageBytes / 16
             int stage = 0; uint32_t phase = 0, dphase = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
@@ -185,8 +202,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                          mbar_wait(afull_bar(stage), phase, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint64_t bdesc = smem_desc_sw128(smem_base + stage * Cfg::kStageBytes);
+                    const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(stage * Cfg::kStageBytes) >> 4);
                     const uint32_t a_tmem = tmem_base + Cfg::kACol + 32 * stage;
+#ifdef W4A16_TC_EXPERIMENT
+                    if (!(W4A16_TC_EXPERIMENT & 2))
+#endif
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
                         mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
@@ -233,7 +253,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 }
                 ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs));
                 if (!ok) break;
+#ifdef W4A16_TC_EXPERIMENT
+                if (has_tile && !(W4A16_TC_EXPERIMENT & 1)) {
+#else
                 if (has_tile) {
+#endif
                     const unsigned char* st = smem + stage * Cfg::kStageBytes;
                     const uint4* wq = reinterpret_cast<const uint4*>(st + Cfg::kXBytes);
                     const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + quarter * 32 + r;
