@@ -45,34 +45,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(suspend_ns) : "memory");
     return ok != 0;
 }
-// Non-blocking probe of a phase.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up; returns
 // false on timeout or when another role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns)
 {
-#ifdef W4A16_WAIT_SPIN
-    // experiment: busy polling with the non-blocking probe only
-    if (mbar_test_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t polls = 0;
-    while (!mbar_test_wait(bar, parity)) {
-        if ((++polls & 1023u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > budget_ns) { *abort_flag = 1; return false; }
-        }
-    }
-    return true;
-#else
     constexpr uint32_t kSuspendNs = 1000000;                 // hint: up to 1 ms per probe
     if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
     const uint64_t t0 = globaltimer_ns();
@@ -85,7 +61,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     return true;
-#endif
 }
 
 // ---- TMA -----------------------------------------------------------------------------------

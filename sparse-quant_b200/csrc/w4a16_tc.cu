@@ -155,8 +155,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 const uint32_t w_bytes = nb_tiles * 512u, zs_bytes = nb_tiles * 128u;
                 const uint32_t tx = Cfg::kXBytes + 2 * w_bytes + zs_bytes;
                 const uint4* wsrc = p.qw + (size_t)(ks0 * 2) * row_words + nb * 4 * 32;
-                int kg = (ks0 * kBlockK) / p.g, in_group = ks0 % steps_per_group;
-                const uint32_t* zsrc = p.zs + (size_t)kg * p.N + nb * kBlockN;
+                int in_group = ks0 % steps_per_group;
+                const uint32_t* zsrc = p.zs + (size_t)((ks0 * kBlockK) / p.g) * p.N + nb * kBlockN;
                 int kcoord = ks0 * kBlockK;
                 for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWaitBudgetNs);
@@ -204,9 +204,6 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                     tc_fence_after_sync();
                     const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(stage * Cfg::kStageBytes) >> 4);
                     const uint32_t a_tmem = tmem_base + Cfg::kACol + 32 * stage;
-#ifdef W4A16_TC_EXPERIMENT
-                    if (!(W4A16_TC_EXPERIMENT & 2))
-#endif
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
                         mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
@@ -253,11 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 }
                 ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs));
                 if (!ok) break;
-#ifdef W4A16_TC_EXPERIMENT
-                if (has_tile && !(W4A16_TC_EXPERIMENT & 1)) {
-#else
                 if (has_tile) {
-#endif
                     const unsigned char* st = smem + stage * Cfg::kStageBytes;
                     const uint4* wq = reinterpret_cast<const uint4*>(st + Cfg::kXBytes);
                     const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + quarter * 32 + r;
