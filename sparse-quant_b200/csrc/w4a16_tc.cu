@@ -8,23 +8,36 @@
 // out-features per CTA tile), the activations are "B" (N = 64/128/256 tokens), the fp32
 // accumulator D[out-feature lane][token column] lives in tensor memory.
 //
-// One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6.. dequantisers, 4 TMA, 5 MMA):
-//   warp 4   TMA producer: per 64-k step one tensor copy of the activation tile (128-byte
-//            swizzle, K-major) plus plain bulk copies of the packed weight tiles (a k-tile row
-//            of the format is contiguous) and of the group's (zero, scale) row; all complete on
-//            one mbarrier per stage.  No cluster fan-out is used anywhere.
-//   warps0-3,6.. dequantisers (groups of four taking k-steps in turn): read 16 B per lane per 32x32 tile from shared memory, expand the
-//            nibbles in registers, (t - z) * s with sub.ftz/mul.ftz (bit-exact with the
-//            reference), and write the fp16 result straight into tensor memory with
-//            tcgen05.st.16x128b - the packed layout is already that fragment order - so the
-//            dequantised weights never touch shared memory.
-//   warp 5   MMA issuer: tcgen05.mma kind::f16 with A from tensor memory and B from the
-//            swizzled shared-memory tile, four K=16 instructions per stage; tcgen05.commit
-//            releases the stage and, after the last step, publishes the accumulator.
-//   warps0-3 epilogue (after their last dequant step of the tile): tcgen05.ld the accumulator,
+// One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6-9 dequantisers, 4 and 10 TMA, 5 MMA).
+//
+// What sets the pace is the ISSUE cost of the tensor-core instructions in the one thread that may issue them
+// (measured on B200 with a loop of nothing but MMAs, 148 CTAs): a tcgen05.mma takes about 94 cycles to issue whatever
+// its N (it executes in N/2 cycles, so only N = 256 hides the issue), and a tcgen05.commit costs about 205 cycles.
+// A pipeline step is therefore 128 k = eight MMAs behind ONE commit (8 x 94 + 205 = 957 issue cycles against 1024
+// cycles of tensor time at 256 tokens); with 64-k steps and one or two commits per step the same kernel ran at
+// 750 to 790 cycles per 512 cycles of tensor time, whatever the token tile, and no change to the other roles moved it.
+//
+// Rings (a stage = 128 k):
+//   x ring   (shared memory, 128-byte swizzle, K-major): the activation tile as two 64-k sub-tiles, filled by warp 4
+//            with two tensor copies on one mbarrier, read only by the MMA.
+//   A ring   (tensor memory, 64 columns per slot, same depth and index as the x ring): the dequantised fp16 weights
+//            of the stage, written by the dequantisers, read by the MMA.  One tcgen05.commit per stage releases the
+//            x stage and the A slot together (barrier `consumed`, waited on by warp 4 and by the dequantisers).
+//   W ring   (shared memory, own depth): the stage's packed weight tiles (a k-tile row of the format is contiguous:
+//            plain bulk copies) and the (zero, scale) row(s), filled by warp 10, read only by the dequantisers and
+//            released as soon as they hold the words in registers.
+//   warps0-3,6-9 dequantisers (two groups of four; group g takes the g-th 64-k half of every stage): read 16 B per
+//            lane per 32x32 tile from shared memory, expand the nibbles in registers, (t - z) * s with
+//            sub.ftz/mul.ftz (bit-exact with the reference), and write the fp16 result straight into tensor memory
+//            with tcgen05.st.16x128b - the packed layout is already that fragment order - so the dequantised weights
+//            never touch shared memory.
+//   warp 5   MMA issuer: tcgen05.mma kind::f16 with A from tensor memory and B from the swizzled shared-memory
+//            tile, eight K=16 instructions per stage; the coming stage's barriers are probed before the MMAs are
+//            issued, so that in steady state no barrier round trip sits between two stages.
+//   warps0-3,6-9 epilogue (after their last dequant step of the tile): tcgen05.ld the accumulator,
 //            fp32 -> fp16, bias add, transposed store to out[token, out-feature].
-// Every mbarrier wait is bounded; on a timeout the CTA raises an error word in global memory,
-// drains and frees its tensor memory, and returns.
+// No cluster fan-out is used anywhere.  Every mbarrier wait is bounded; on a timeout the CTA raises an error word
+// in global memory, drains and frees its tensor memory, and returns.
 #include <mutex>
 
 #include <cuda.h>
@@ -39,33 +52,31 @@ using namespace sm100;
 namespace {
 
 constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 packed tiles)
-constexpr int kBlockK   = 64;                  // k per stage (2 packed tiles)
-// Measured on B200 (M = 8192): 2 groups 1136 / 1148 / 1256 TFLOP/s, 4 groups 1104 / 1111 / 1206 - the dequantisers are
-// not the limit once two steps are in flight (under the power cap the SM clock, not the issue rate, sets the pace).
-#ifndef W4A16_TC_DEQUANT_GROUPS
-#define W4A16_TC_DEQUANT_GROUPS 2
-#endif
-constexpr int kDequantGroups = W4A16_TC_DEQUANT_GROUPS;    // groups of four dequantiser warps taking k-steps in turn
-constexpr int kThreads  = 64 + 128 * kDequantGroups;       // warps 0-3, 6-9, 10-13, ...: dequantisers; warp 4: TMA; warp 5: MMA
+constexpr int kBlockK   = 128;                 // k per pipeline stage (4 packed tiles, eight MMAs, one commit)
+constexpr int kSubK     = 64;                  // k per swizzled activation sub-tile (128 bytes of fp16)
+constexpr int kDequantGroups = 2;              // groups of four dequantiser warps, one per 64-k half of a stage
+constexpr int kWProducerWarp = 2 + 4 * kDequantGroups;     // warp 10
+constexpr int kThreads  = 32 * (kWProducerWarp + 1);       // warps 0-3, 6-9: dequantisers; 4: x TMA; 5: MMA; 10: W TMA
 constexpr int kTmemCols = 512;
-#ifndef W4A16_TC_STAGES_256
-#define W4A16_TC_STAGES_256 6
-#endif
 constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;   // 0.4 s: far above any legitimate wait
 
 template <int TOK>
 struct TcCfg {
-    // as many stages as shared memory (227 KB) and the TMEM A ring allow: the pipeline is latency-bound when few
-    // tiles share the machine, so bytes in flight per SM matter (all variants exceed 113 KB: one CTA per SM)
-    static constexpr int kStages   = TOK == 256 ? W4A16_TC_STAGES_256 : (TOK == 128 ? 10 : 14);
-    static constexpr int kXBytes   = TOK * kBlockK * 2;
-    static constexpr int kWBytes   = 2 * 4 * 512;
-    static constexpr int kStageBytes = kXBytes + kWBytes + 1024;     // zs padded to keep 1024-B alignment
+    static constexpr int kXSubBytes = TOK * kSubK * 2;                // one 64-k sub-tile (multiple of 8 KB)
+    static constexpr int kXBytes   = 2 * kXSubBytes;                  // activation tile of a stage
+    static constexpr int kWBytes   = 4 * 4 * 512;                     // four k-tile rows of four packed tiles
+    static constexpr int kWStageBytes = kWBytes + 1024;               // + up to two (zero, scale) rows of 128 out-features
+    static constexpr int kWStages  = TOK == 256 ? 3 : 4;
+    static constexpr int kStages   = TOK == 256 ? 3 : (TOK == 128 ? 5 : 6);   // x ring == A ring
+    static constexpr int kBarrierBytes = 1024;
     static constexpr int kACol     = TOK;                             // first TMEM column of the A ring
-    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 512 /*barriers*/;
-    static_assert(8 * (3 * kStages + 3) + 12 <= 512, "barrier area");
+    static constexpr int kWRingOff = kStages * kXBytes;
+    static constexpr int kBarOff   = kWRingOff + kWStages * kWStageBytes;
+    static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kBarOff + kBarrierBytes;
+    static constexpr int kBarriers = 3 * kStages + 2 * kWStages + 3;
+    static_assert(8 * kBarriers + 12 <= kBarrierBytes, "barrier area");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-    static_assert(kACol + 32 * kStages <= kTmemCols, "TMEM budget");
+    static_assert(kACol + 64 * kStages <= kTmemCols, "TMEM budget");
 };
 
 struct TcParams {
@@ -87,29 +98,29 @@ template <int TOK>
 __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p)
 {
     using Cfg = TcCfg<TOK>;
-    constexpr int S = Cfg::kStages;
+    constexpr int S = Cfg::kStages, SW = Cfg::kWStages;
     extern __shared__ unsigned char smem_raw[];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + S * Cfg::kStageBytes;
-    // barrier layout (8 B each): full[S], afull[S], empty[S], dfull, dempty, epi ; then tmem ptr, abort flag, last flag
-    auto full_bar  = [&](int s) { return bar_base + 8u * s; };
-    auto afull_bar = [&](int s) { return bar_base + 8u * (S + s); };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-    const uint32_t dfull_bar = bar_base + 8u * (3 * S), dempty_bar = bar_base + 8u * (3 * S + 1), epi_bar = bar_base + 8u * (3 * S + 2);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S * Cfg::kStageBytes + 8 * (3 * S + 3));
+    const uint32_t bar_base = smem_base + Cfg::kBarOff;
+    // barrier layout (8 B each): xfull[S], afull[S], consumed[S], wfull[SW], wempty[SW], dfull, dempty, epi ; then
+    // tmem ptr, abort flag, last flag
+    auto xfull_bar    = [&](int s) { return bar_base + 8u * s; };
+    auto afull_bar    = [&](int s) { return bar_base + 8u * (S + s); };
+    auto consumed_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
+    auto wfull_bar    = [&](int s) { return bar_base + 8u * (3 * S + s); };
+    auto wempty_bar   = [&](int s) { return bar_base + 8u * (3 * S + SW + s); };
+    const uint32_t dfull_bar = bar_base + 8u * (Cfg::kBarriers - 3), dempty_bar = dfull_bar + 8u, epi_bar = dfull_bar + 16u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kBarOff + 8 * Cfg::kBarriers);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(afull_bar(s), 4);
-            mbar_init(empty_bar(s), 1);
-        }
+        for (int s = 0; s < S; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(afull_bar(s), 8); mbar_init(consumed_bar(s), 1); }
+        for (int s = 0; s < SW; ++s) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 8); }
         mbar_init(dfull_bar, 1);
         mbar_init(dempty_bar, 8);
         mbar_init(epi_bar, 8);
@@ -134,63 +145,89 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         ks0 = (int)((long long)k_steps * kp / p.split);
         ks1 = (int)((long long)k_steps * (kp + 1) / p.split);
     };
+    // after a failed wait: give copies already in flight time to land before the CTA releases its shared memory
+    auto drain_copies = [&]() {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000) { }
+    };
 
     if (warp == 4) {
-        // ------------------------------ TMA producer ------------------------------
-        // Three lanes share the copies of a stage, so that the address arithmetic and issue latency of one thread is
-        // not what paces the pipeline: lane 0 arms the barrier and fetches the activation tile, lane 1 the two rows of
-        // packed tiles, lane 2 the group's (zero, scale) row.  Copies that complete before lane 0 has armed the
-        // barrier only drive its byte count negative for a moment; the phase cannot complete before lane 0's arrival.
+        // ------------------------------ TMA producer of the activation tiles ------------------------------
+        if (lane == 0) {
+            int st = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const int tb = (item / p.split) / p.n_blocks;
+                int ks0, ks1;
+                k_range(item, ks0, ks1);
+                int kcoord = ks0 * kBlockK;
+                for (int ks = ks0; ks < ks1; ++ks) {
+                    ok = mbar_wait(consumed_bar(st), phase ^ 1u, abort_flag, kWaitBudgetNs);
+                    if (!ok) break;
+                    const uint32_t bar = xfull_bar(st);
+                    const uint32_t dst = smem_base + st * Cfg::kXBytes;
+                    mbar_arrive_expect_tx(bar, Cfg::kXBytes);
+                    tma_load_2d(dst, &x_map, kcoord, tb * TOK, bar);
+                    tma_load_2d(dst + Cfg::kXSubBytes, &x_map, kcoord + kSubK, tb * TOK, bar);
+                    kcoord += kBlockK;
+                    if (++st == S) { st = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) drain_copies();
+        }
+    } else if (warp == kWProducerWarp) {
+        // ------------------------------ TMA producer of the packed weights ------------------------------
+        // Three lanes share the copies of a stage (an issued copy holds its thread for about a hundred cycles).  A
+        // copy that completes before lane 0 has armed the barrier only drives its byte count negative for a moment;
+        // the phase cannot complete before lane 0's arrival.
         if (lane < 3) {
-            int stage = 0; uint32_t phase = 0;
+            int sw = 0; uint32_t wphase = 0;
             bool ok = true;
             const uint32_t row_words = (uint32_t)n_tiles * 32u;                 // uint4 per k-tile row of the packed matrix
-            const int steps_per_group = p.g / kBlockK;                          // 1 or 2 (g = 64 or 128)
+            const int zs_rows = kBlockK / p.g;                                  // 1 (g = 128) or 2 (g = 64) per stage
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
-                const int tile = item / p.split;
-                const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
+                const int nb = (item / p.split) % p.n_blocks;
                 const int nb_tiles = min(4, n_tiles - nb * 4);
                 int ks0, ks1;
                 k_range(item, ks0, ks1);
                 const uint32_t w_bytes = nb_tiles * 512u, zs_bytes = nb_tiles * 128u;
-                const uint32_t tx = Cfg::kXBytes + 2 * w_bytes + zs_bytes;
-                const uint4* wsrc = p.qw + (size_t)(ks0 * 2) * row_words + nb * 4 * 32;
-                int in_group = ks0 % steps_per_group;
-                const uint32_t* zsrc = p.zs + (size_t)((ks0 * kBlockK) / p.g) * p.N + nb * kBlockN;
-                int kcoord = ks0 * kBlockK;
+                const uint4* wsrc = p.qw + (size_t)(ks0 * 4) * row_words + nb * 4 * 32;
+                const uint32_t* zsrc = p.zs + (size_t)(ks0 * zs_rows) * p.N + nb * kBlockN;
                 for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWaitBudgetNs);
+                    ok = mbar_wait(wempty_bar(sw), wphase ^ 1u, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
-                    const uint32_t st = smem_base + stage * Cfg::kStageBytes;
-                    const uint32_t bar = full_bar(stage);
+                    const uint32_t dst = smem_base + Cfg::kWRingOff + sw * Cfg::kWStageBytes;
+                    const uint32_t bar = wfull_bar(sw);
                     if (lane == 0) {
-                        mbar_arrive_expect_tx(bar, tx);
-                        tma_load_2d(st, &x_map, kcoord, tb * TOK, bar);
+                        mbar_arrive_expect_tx(bar, 4 * w_bytes + zs_rows * zs_bytes);
+                        bulk_load(dst, wsrc, w_bytes, bar);
+                        bulk_load(dst + 2048, wsrc + row_words, w_bytes, bar);
                     } else if (lane == 1) {
-                        bulk_load(st + Cfg::kXBytes, wsrc, w_bytes, bar);
-                        bulk_load(st + Cfg::kXBytes + 2048, wsrc + row_words, w_bytes, bar);
+                        bulk_load(dst + 4096, wsrc + 2 * row_words, w_bytes, bar);
+                        bulk_load(dst + 6144, wsrc + 3 * row_words, w_bytes, bar);
                     } else {
-                        bulk_load(st + Cfg::kXBytes + Cfg::kWBytes, zsrc, zs_bytes, bar);
+                        bulk_load(dst + Cfg::kWBytes, zsrc, zs_bytes, bar);
+                        if (zs_rows == 2) bulk_load(dst + Cfg::kWBytes + 512, zsrc + p.N, zs_bytes, bar);
                     }
-                    wsrc += 2 * row_words;
-                    kcoord += kBlockK;
-                    if (++in_group == steps_per_group) { in_group = 0; zsrc += p.N; }
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                    wsrc += 4 * row_words;
+                    zsrc += (size_t)zs_rows * p.N;
+                    if (++sw == SW) { sw = 0; wphase ^= 1u; }
                 }
             }
-            if (!ok && lane == 0) {
-                // give copies already in flight time to land before the CTA releases its shared memory
-                const uint64_t t0 = globaltimer_ns();
-                while (globaltimer_ns() - t0 < 200000) { }
-            }
+            if (!ok && lane == 0) drain_copies();
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16_m128(TOK);
-            const uint64_t bdesc0 = smem_desc_sw128(smem_base);        // stage s: the start-address field advances by s * kStageBytes / 16
-            int stage = 0; uint32_t phase = 0, dphase = 0;
+            const uint64_t bdesc0 = smem_desc_sw128(smem_base);        // the start-address field advances in 16-byte units
+            int st = 0; uint32_t phase = 0, dphase = 0;
             bool ok = true;
+            // Whatever this thread does between the last MMA of a stage and the first of the next is idle tensor
+            // time, and a barrier wait that succeeds at once still costs a round trip of about a hundred cycles.  The
+            // coming stage's two barriers are therefore probed before this stage's MMAs; in steady state both are
+            // complete (every other role runs ahead of the MMA) and the next iteration starts issuing at once.
+            bool ready = false;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 ok = mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs);   // epilogue drained D
                 if (!ok) break;
@@ -198,17 +235,24 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 int ks0, ks1;
                 k_range(item, ks0, ks1);
                 for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs) &&
-                         mbar_wait(afull_bar(stage), phase, abort_flag, kWaitBudgetNs);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs) &&
+                             mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs);
+                        if (!ok) break;
+                    }
                     tc_fence_after_sync();
-                    const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(stage * Cfg::kStageBytes) >> 4);
-                    const uint32_t a_tmem = tmem_base + Cfg::kACol + 32 * stage;
+                    const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(st * Cfg::kXBytes) >> 4);
+                    const uint32_t a_tmem = tmem_base + Cfg::kACol + 64 * st;
+                    const int cur = st;
+                    if (++st == S) { st = 0; phase ^= 1u; }
+                    const bool next_a = mbar_test_wait(afull_bar(st), phase);
+                    const bool next_x = mbar_test_wait(xfull_bar(st), phase);
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
-                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
-                    tc_commit(empty_bar(stage));
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (Cfg::kXSubBytes >> 4) + 2 * (kk & 3)),
+                                   idesc, ((ks - ks0) | kk) != 0);
+                    tc_commit(consumed_bar(cur));
+                    ready = next_a && next_x;
                 }
                 if (!ok) break;
                 tc_commit(dfull_bar);
@@ -216,18 +260,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             }
         }
     } else {
-        // ------------------------------ dequant + epilogue (warps 0..3 and 6..) ------------------------------
-        // kDequantGroups groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which
-        // is also the packed tile column it dequantises.  Group g takes the k-steps with (step % groups) == g
-        // (counted across tiles, so the rotation follows the stage ring): one step keeps a warp busy for a chain of
-        // dependent latencies (shared-memory load, unpack, sub/mul, tcgen05.st, its completion), so the dequant
-        // rate is set by how many steps are in flight, not by issue slots.  Groups 0 and 1 also drain the
-        // accumulator (half of the columns each) in the epilogue; the others run ahead into the next tile.
-        int stage = 0; uint32_t phase = 0, dphase = 0;
+        // ------------------------------ dequant + epilogue (warps 0..3 and 6..9) ------------------------------
+        // Two groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which is also the
+        // packed tile column it dequantises.  Group g takes the g-th 64-k half of every stage: a half keeps a warp
+        // busy for a chain of dependent latencies (shared-memory load, unpack, sub/mul, tcgen05.st, its completion),
+        // which the ring depth covers.  Both groups also drain the accumulator (half of the columns each) in the
+        // epilogue.
+        int st = 0, sw = 0; uint32_t phase = 0, wphase = 0, dphase = 0;
         bool ok = true;
         const int r = lane >> 2;
-        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : (warp - 2) / 4;
-        uint32_t step_mod = 0, epi_phase = 0;
+        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : 1;
+        uint32_t epi_phase = 0;
         // bounded rendezvous of the eight dequant/epilogue warps (split-K finalisation)
         auto epi_sync = [&]() -> bool {
             __syncwarp();
@@ -237,30 +280,38 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             return done;
         };
         const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
+        const int zs_row = p.g == 64 ? dgroup : 0;                     // (zero, scale) row of this group's half
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
             const int tile = item / p.split, kp = item % p.split;
             const int nb = tile % p.n_blocks, tb = tile / p.n_blocks;
             const bool has_tile = nb * 4 + quarter < n_tiles;
             int ks0, ks1;
             k_range(item, ks0, ks1);
-            for (int ks = ks0; ks < ks1; ++ks, step_mod = (step_mod + 1 == (uint32_t)kDequantGroups ? 0u : step_mod + 1)) {
-                if (step_mod != (uint32_t)dgroup) {                    // another group's stage
-                    if (++stage == S) { stage = 0; phase ^= 1u; }
-                    continue;
+            for (int ks = ks0; ks < ks1; ++ks) {
+                ok = __all_sync(0xffffffffu, mbar_wait(wfull_bar(sw), wphase, abort_flag, kWaitBudgetNs));
+                if (!ok) break;
+                const unsigned char* wst = smem + Cfg::kWRingOff + sw * Cfg::kWStageBytes;
+                const uint4* wq = reinterpret_cast<const uint4*>(wst) + dgroup * 256;
+                const uint32_t* zsp = reinterpret_cast<const uint32_t*>(wst + Cfg::kWBytes + zs_row * 512) + quarter * 32 + r;
+                uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
+                uint32_t zsw[4] = {0, 0, 0, 0};
+                if (has_tile) {
+                    q0 = wq[quarter * 32 + lane]; q1 = wq[128 + quarter * 32 + lane];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) zsw[j] = zsp[8 * j];
                 }
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, kWaitBudgetNs));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(wempty_bar(sw));                // the words are in registers: the stage may refill
+                ok = __all_sync(0xffffffffu, mbar_wait(consumed_bar(st), phase ^ 1u, abort_flag, kWaitBudgetNs));
                 if (!ok) break;
                 if (has_tile) {
-                    const unsigned char* st = smem + stage * Cfg::kStageBytes;
-                    const uint4* wq = reinterpret_cast<const uint4*>(st + Cfg::kXBytes);
-                    const uint32_t* zsp = reinterpret_cast<const uint32_t*>(st + Cfg::kXBytes + Cfg::kWBytes) + quarter * 32 + r;
-                    const uint4 q0 = wq[quarter * 32 + lane], q1 = wq[128 + quarter * 32 + lane];
+                    tc_fence_after_sync();
                     const uint32_t words[2][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}};
 #pragma unroll
                     for (int nh = 0; nh < 2; ++nh) {
                         uint32_t z0, s0, z1, s1;
-                        split_zs(zsp[nh * 16], z0, s0);
-                        split_zs(zsp[nh * 16 + 8], z1, s1);
+                        split_zs(zsw[nh * 2], z0, s0);
+                        split_zs(zsw[nh * 2 + 1], z1, s1);
                         uint32_t a[16];
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
@@ -274,17 +325,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                                 d[2] = dequant_h2(h[2], z0, s0);
                                 d[3] = dequant_h2(h[3], z1, s1);
                             }
-                        tmem_st_16x128b_x8(tmem_base + lane_field + ((uint32_t)(nh * 16) << 16) + Cfg::kACol + 32 * stage, a);
+                        tmem_st_16x128b_x8(tmem_base + lane_field + ((uint32_t)(nh * 16) << 16) + Cfg::kACol + 64 * st + 32 * dgroup, a);
                     }
                     tmem_wait_st();
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(afull_bar(stage));
-                if (++stage == S) { stage = 0; phase ^= 1u; }
+                if (lane == 0) mbar_arrive(afull_bar(st));
+                if (++sw == SW) { sw = 0; wphase ^= 1u; }
+                if (++st == S) { st = 0; phase ^= 1u; }
             }
             if (!ok) break;
-            if (dgroup >= 2) continue;                                   // only groups 0 and 1 drain the accumulator
 
             // epilogue: thread = out-feature (TMEM lane), registers = tokens
             ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, dphase, abort_flag, kWaitBudgetNs));
@@ -425,10 +476,10 @@ int g_force_tok = 0, g_force_split = 0;
 
 struct TcPlan { int tok, split; };
 
-// Token tile and K split by a cost model in SM clocks (at the nominal clock), fitted to measurements on B200: a work
-// item costs k-steps x step + epilogue, where a 64-k step was measured at about 800 + 0.6 x tokens clocks whatever the
-// token tile (the MMA alone would need 2 x tokens), items run in waves of one per SM, and split-K adds the round trip
-// of the fp32 partial tiles through L2/HBM at about 650 bytes per clock.
+// Token tile and K split by a cost model in SM clocks, fitted to measurements on B200: a work item costs
+// k-steps x step + epilogue, where a 128-k step costs the larger of its tensor time (4 x tokens) and the issue time of
+// its eight MMAs and one commit, items run in waves of one per SM, and split-K adds the round trip of the fp32
+// partial tiles through L2/HBM at about 650 bytes per clock.
 TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0)
 {
     const int n_blocks = (N + kBlockN - 1) / kBlockN;
@@ -441,13 +492,13 @@ TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0
         if (g_force_tok && t != g_force_tok) continue;
         for (int sp = 1; sp <= 4; sp *= 2) {
             if (g_force_split && !force_split ? sp != g_force_split : (sp > 1 && !allow_split)) continue;
-            if (sp > 1 && k_steps / sp < 8) continue;
+            if (sp > 1 && k_steps / sp < 4) continue;
             if (sp > 1 && K < 8192 && !g_force_split && !force_split) continue;      // measured: no gain from splitting a short K
             if (force_split && sp != force_split) continue;
             const long long items = (long long)n_blocks * ((tokens + t - 1) / t) * sp;
             const long long waves = (items + 147) / 148;
-            const double measured = 800.0 + 0.6 * t;
-            const double step = 2.0 * t > measured ? 2.0 * t : measured;
+            const double issue = 8 * 94.0 + 205.0 + 60.0;           // eight MMAs, one commit, the loop around them
+            const double step = 4.0 * t > issue ? 4.0 * t : issue;
             double cost = waves * ((double)(k_steps / sp) * step + 6.0 * t + 2000);
             if (sp > 1) cost += (double)sp * tokens * N * 8.0 / 650.0 + 3000;        // partials written + read back
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {t, sp}; }
@@ -508,7 +559,7 @@ int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaSt
     CUtensorMap map;
     {
         const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.tokens};
-        const uint32_t box[2] = {(uint32_t)kBlockK, (uint32_t)tok};
+        const uint32_t box[2] = {(uint32_t)kSubK, (uint32_t)tok};
         int s = encode_tensor_map_2d(&map, a.x, 2, dims, (uint64_t)a.K * sizeof(__half), box, /*swizzle128*/ true);
         if (s != W4A16_OK) return s;
     }
@@ -576,7 +627,7 @@ extern "C" int w4a16_gemm_static_scratch(const void* x, const void* qweight, con
 {
     using namespace w4a16;
     if (group_size != 64 && group_size != 128) return W4A16_ERR_GROUP_SIZE;
-    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || K < 1024) return W4A16_ERR_BAD_SHAPE;
+    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || (K % 128) || K < 1024) return W4A16_ERR_BAD_SHAPE;
     if (!x || !qweight || !zeros_scales || !out) return W4A16_ERR_NULL_POINTER;
     if (((uintptr_t)x & 15) || ((uintptr_t)qweight & 15) || ((uintptr_t)zeros_scales & 15) || ((uintptr_t)out & 15))
         return W4A16_ERR_MISALIGNED;
