@@ -16,8 +16,8 @@
  *   out           fp16   [tokens, N]
  *   bias          fp16   [N] or NULL
  * Constraints: N % 32 == 0, K % g == 0, g in {32, 64, 128}, tokens >= 0; x, qweight,
- * zeros_scales and out 16-byte aligned.  The tcgen05 kernel additionally needs g in {64, 128} and
- * K % 128 == 0; W4A16_ALGO_AUTO falls back to the skinny kernel otherwise.
+ * zeros_scales and out 16-byte aligned.  The tcgen05 kernel additionally needs g in {64, 128};
+ * W4A16_ALGO_AUTO falls back to the skinny kernel otherwise.
  */
 #ifndef W4A16_B200_H_
 #define W4A16_B200_H_
@@ -264,7 +264,7 @@ int w4a16_silu_mul(const void* gate_up, void* out, int rows, int n, void* stream
  * with a memory budget pinned at start-up): the fp32 partial tiles, the arrival counters and the
  * error word live in a file-scope device array of the library (about 16 MiB per GPU that loads the
  * library, held until the process exits).  Nothing is allocated or freed, no workspace argument.
- * Limits: 2 * tokens * N * 4 bytes <= 16 MiB and at most 4096 output tiles, K >= 1024, K % 128 == 0, g in {64, 128};
+ * Limits: 2 * tokens * N * 4 bytes <= 16 MiB and at most 4096 output tiles, K >= 1024, g in {64, 128};
  * beyond that W4A16_ERR_TOO_LARGE / W4A16_ERR_BAD_SHAPE.  All calls on a device share the array:
  * calls whose kernels could overlap on the GPU (different streams) must be serialised by the caller.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and clears

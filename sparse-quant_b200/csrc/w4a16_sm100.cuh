@@ -72,6 +72,17 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// One lane of a converged warp, chosen by the hardware.  Code that issues tcgen05/TMA instructions should let the
+// WHOLE warp walk its loop and put only the instructions under this predicate: the operands then live in uniform
+// registers.  Measured: a loop that a single lane enters (if (lane == 0) { for ... }) issues a tcgen05.mma every
+// 94 cycles, the same loop walked by the warp with an elected issuer every 45.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar)
 {

@@ -218,46 +218,50 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = idesc_f16_m128(TOK);
-            const uint64_t bdesc0 = smem_desc_sw128(smem_base);        // the start-address field advances in 16-byte units
-            int st = 0; uint32_t phase = 0, dphase = 0;
-            bool ok = true;
-            // Whatever this thread does between the last MMA of a stage and the first of the next is idle tensor
-            // time, and a barrier wait that succeeds at once still costs a round trip of about a hundred cycles.  The
-            // coming stage's two barriers are therefore probed before this stage's MMAs; in steady state both are
-            // complete (every other role runs ahead of the MMA) and the next iteration starts issuing at once.
-            bool ready = false;
-            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
-                ok = mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs);   // epilogue drained D
-                if (!ok) break;
+        // The whole warp walks the loop and an elected lane issues, so that descriptors and addresses stay in uniform
+        // registers (see elect_one).
+        constexpr uint32_t idesc = idesc_f16_m128(TOK);
+        const uint64_t bdesc0 = smem_desc_sw128(smem_base);            // the start-address field advances in 16-byte units
+        int st = 0; uint32_t phase = 0, dphase = 0;
+        bool ok = true;
+        // Whatever this warp does between the last MMA of a stage and the first of the next is idle tensor time, and
+        // a barrier wait that succeeds at once still costs a round trip of about a hundred cycles.  The coming stage's
+        // two barriers are therefore probed before this stage's MMAs; in steady state both are complete (every other
+        // role runs ahead of the MMA) and the next iteration starts issuing at once.
+        bool ready = false;
+        for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            ok = __all_sync(0xffffffffu, mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs));   // epilogue drained D
+            if (!ok) break;
+            tc_fence_after_sync();
+            int ks0, ks1;
+            k_range(item, ks0, ks1);
+            for (int ks = ks0; ks < ks1; ++ks) {
+                if (!ready) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs) &&
+                                                 mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs));
+                    if (!ok) break;
+                }
                 tc_fence_after_sync();
-                int ks0, ks1;
-                k_range(item, ks0, ks1);
-                for (int ks = ks0; ks < ks1; ++ks) {
-                    if (!ready) {
-                        ok = mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs) &&
-                             mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs);
-                        if (!ok) break;
-                    }
-                    tc_fence_after_sync();
-                    const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(st * Cfg::kXBytes) >> 4);
-                    const uint32_t a_tmem = tmem_base + Cfg::kACol + 64 * st;
-                    const int cur = st;
-                    if (++st == S) { st = 0; phase ^= 1u; }
-                    const bool next_a = mbar_test_wait(afull_bar(st), phase);
-                    const bool next_x = mbar_test_wait(xfull_bar(st), phase);
+                const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(st * Cfg::kXBytes) >> 4);
+                const uint32_t a_tmem = tmem_base + Cfg::kACol + 64 * st;
+                const int cur = st;
+                if (++st == S) { st = 0; phase ^= 1u; }
+                const bool next_a = mbar_test_wait(afull_bar(st), phase);
+                const bool next_x = mbar_test_wait(xfull_bar(st), phase);
+                if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < kBlockK / 16; ++kk)
                         mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (Cfg::kXSubBytes >> 4) + 2 * (kk & 3)),
                                    idesc, ((ks - ks0) | kk) != 0);
                     tc_commit(consumed_bar(cur));
-                    ready = next_a && next_x;
                 }
-                if (!ok) break;
-                tc_commit(dfull_bar);
-                dphase ^= 1u;
+                __syncwarp();
+                ready = __all_sync(0xffffffffu, next_a && next_x);
             }
+            if (!ok) break;
+            if (elect_one()) tc_commit(dfull_bar);
+            __syncwarp();
+            dphase ^= 1u;
         }
     } else {
         // ------------------------------ dequant + epilogue (warps 0..3 and 6..9) ------------------------------
@@ -337,33 +341,50 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             }
             if (!ok) break;
 
-            // epilogue: thread = out-feature (TMEM lane), registers = tokens
+            // epilogue: thread = out-feature (TMEM lane), registers = tokens.  The per-element loops carry no branch
+            // (measured: with the bias / ReLU / residual / ragged-tile tests inside them a tile took 15 000 cycles to
+            // drain, without them 5 000): the common case - full token tile, no ReLU, no residual - has its own loop,
+            // and a missing bias is added as -0.0, which changes no value.
             ok = __all_sync(0xffffffffu, mbar_wait(dfull_bar, dphase, abort_flag, kWaitBudgetNs));
             if (!ok) break;
             dphase ^= 1u;
             tc_fence_after_sync();
             const int n = nb * kBlockN + quarter * 32 + lane;
             const bool n_ok = n < p.N;
-            const __half bias = (p.bias && n_ok) ? p.bias[n] : __half();
+            const __half bias = (p.bias && n_ok) ? p.bias[n] : __ushort_as_half((unsigned short)0x8000u);
             const int tok0 = tb * TOK;
+            const bool full_tile = tok0 + TOK <= p.tokens;
+            const bool plain = full_tile && !p.relu && !p.residual;
+            const int c_begin = dgroup * (TOK / 2), c_end = (dgroup + 1) * (TOK / 2);
+            // the accumulator is free again once this warp's columns are in registers: the MMA of the next tile
+            // starts while the values are still being converted and stored
+            auto release_accumulator = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty_bar);
+            };
+            auto finish = [&](float acc, int t) {                                // general path: one output element
+                __half h = __hadd(__float2half_rn(acc), bias);
+                if (p.relu) h = __hmax(h, __half());
+                if (p.residual) h = __hadd(h, p.residual[(size_t)t * p.N + n]);
+                p.out[(size_t)t * p.N + n] = h;
+            };
             if (p.split == 1) {
 #pragma unroll 1
-                for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
+                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
                     tmem_wait_ld();
-                    if (n_ok) {
+                    if (c0 + 32 >= c_end) release_accumulator();
+                    if (!n_ok) continue;
+                    if (plain) {
+                        __half* dst = p.out + (size_t)(tok0 + c0) * p.N + n;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int t = tok0 + c0 + j;
-                            if (t < p.tokens) {
-                                __half h = __float2half_rn(__uint_as_float(v[j]));
-                                if (p.bias) h = __hadd(h, bias);
-                                if (p.relu) h = __hmax(h, __half());
-                                if (p.residual) h = __hadd(h, p.residual[(size_t)t * p.N + n]);
-                                p.out[(size_t)t * p.N + n] = h;
-                            }
-                        }
+                        for (int j = 0; j < 32; ++j) dst[(size_t)j * p.N] = __hadd(__float2half_rn(__uint_as_float(v[j])), bias);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (tok0 + c0 + j < p.tokens) finish(__uint_as_float(v[j]), tok0 + c0 + j);
                     }
                 }
             } else {
@@ -371,16 +392,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 // of `split` arrivals, found with one atomic per CTA) adds the parts in a fixed order - deterministic.
                 float* mine = p.partial + (size_t)kp * p.tokens * p.N;
 #pragma unroll 1
-                for (int c0 = dgroup * (TOK / 2); c0 < (dgroup + 1) * (TOK / 2); c0 += 32) {
+                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + lane_field + c0, v);
                     tmem_wait_ld();
-                    if (n_ok) {
+                    if (c0 + 32 >= c_end) release_accumulator();
+                    if (!n_ok) continue;
+                    float* dst = mine + (size_t)(tok0 + c0) * p.N + n;
+                    if (full_tile) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int t = tok0 + c0 + j;
-                            if (t < p.tokens) mine[(size_t)t * p.N + n] = __uint_as_float(v[j]);
-                        }
+                        for (int j = 0; j < 32; ++j) dst[(size_t)j * p.N] = __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (tok0 + c0 + j < p.tokens) dst[(size_t)j * p.N] = __uint_as_float(v[j]);
                     }
                 }
                 __threadfence();
@@ -395,35 +420,32 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 if (*last_flag) {
                     __threadfence();
                     if (n_ok) {
+                        const int c_last = min(c_end, p.tokens - tok0);      // ragged tile: stop at the last token
 #pragma unroll 1
-                        for (int c = dgroup * (TOK / 2); c < (dgroup + 1) * (TOK / 2); c += 8) {
+                        for (int c = c_begin; c < c_last; c += 8) {
                             float v[4][8];                                   // up to 4 parts x 8 tokens in flight
+                            const float* src = p.partial + (size_t)(tok0 + c) * p.N + n;
+                            const bool whole = c + 8 <= c_last;
 #pragma unroll
                             for (int q = 0; q < 4; ++q)
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    const int t = tok0 + c + j;
-                                    v[q][j] = (q < p.split && t < p.tokens) ? __ldcg(p.partial + ((size_t)q * p.tokens + t) * p.N + n) : 0.f;
-                                }
+                                for (int j = 0; j < 8; ++j)
+                                    v[q][j] = (q < p.split && (whole || c + j < c_last)) ? __ldcg(src + ((size_t)q * p.tokens + j) * p.N) : 0.f;
+                            if (whole && plain) {
+                                __half* dst = p.out + (size_t)(tok0 + c) * p.N + n;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int t = tok0 + c + j;
-                                if (t < p.tokens) {
-                                    __half h = __float2half_rn(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j]);
-                                    if (p.bias) h = __hadd(h, bias);
-                                    if (p.relu) h = __hmax(h, __half());
-                                    if (p.residual) h = __hadd(h, p.residual[(size_t)t * p.N + n]);
-                                    p.out[(size_t)t * p.N + n] = h;
-                                }
+                                for (int j = 0; j < 8; ++j)
+                                    dst[(size_t)j * p.N] = __hadd(__float2half_rn(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j]), bias);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (c + j < c_last) finish(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j], tok0 + c + j);
                             }
                         }
                     }
                 }
                 if (!(ok = epi_sync())) break;                               // last_flag may be rewritten by the next item
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dempty_bar);
         }
     }
 
