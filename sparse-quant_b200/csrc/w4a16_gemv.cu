@@ -340,7 +340,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
                 }
             }
             __syncwarp();                                   // every lane is done reading the unit's slot
-            if (lane == 0) {
+            if (sm100::elect_one()) {
                 if (i + depth < n_units) { issue_w(i + depth, slot); issue_x(i + depth, slot); }
                 if (i + depth + p.ahead < n_units) prefetch_w(i + depth + p.ahead);
             }

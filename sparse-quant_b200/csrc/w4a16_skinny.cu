@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             else
                 acc[0][0][0] += __uint_as_float(ring[slot].tiles[0][lane].x & 0x3fu);
             __syncwarp();                                   // every lane is done reading the slot
-            if (lane == 0 && i + depth < n_units)
+            if (i + depth < n_units && sm100::elect_one())
                 issue_unit<G, kUnitK>(ring_addr + slot * (uint32_t)sizeof(SlotT), bars + 8 * slot, &wmap, zs_next + (size_t)(i + depth) * zs_step, p.N,
                               u + depth, nt, groups);
             if (++slot == depth) { slot = 0; phase ^= 1u; }

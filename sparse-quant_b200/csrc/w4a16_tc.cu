@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_tiles = p.N / kTileN;
-    const int k_steps = p.K / kBlockK;
+    const int k_steps = (p.K + kBlockK - 1) / kBlockK;        // K % 128 == 64: the last stage carries one 64-k half
+    const bool k_tail = (p.K % kBlockK) != 0;
     const int total_tiles = p.n_blocks * p.t_blocks * p.split;      // work items: (output tile, K part)
     auto k_range = [&](int item, int& ks0, int& ks1) {
         const int kp = item % p.split;
@@ -198,16 +199,19 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                     if (!ok) break;
                     const uint32_t dst = smem_base + Cfg::kWRingOff + sw * Cfg::kWStageBytes;
                     const uint32_t bar = wfull_bar(sw);
+                    const bool tail = k_tail && ks == k_steps - 1;                  // only the first half exists (g = 64)
                     if (lane == 0) {
-                        mbar_arrive_expect_tx(bar, 4 * w_bytes + zs_rows * zs_bytes);
+                        mbar_arrive_expect_tx(bar, tail ? 2 * w_bytes + zs_bytes : 4 * w_bytes + zs_rows * zs_bytes);
                         bulk_load(dst, wsrc, w_bytes, bar);
                         bulk_load(dst + 2048, wsrc + row_words, w_bytes, bar);
                     } else if (lane == 1) {
-                        bulk_load(dst + 4096, wsrc + 2 * row_words, w_bytes, bar);
-                        bulk_load(dst + 6144, wsrc + 3 * row_words, w_bytes, bar);
+                        if (!tail) {
+                            bulk_load(dst + 4096, wsrc + 2 * row_words, w_bytes, bar);
+                            bulk_load(dst + 6144, wsrc + 3 * row_words, w_bytes, bar);
+                        }
                     } else {
                         bulk_load(dst + Cfg::kWBytes, zsrc, zs_bytes, bar);
-                        if (zs_rows == 2) bulk_load(dst + Cfg::kWBytes + 512, zsrc + p.N, zs_bytes, bar);
+                        if (zs_rows == 2 && !tail) bulk_load(dst + Cfg::kWBytes + 512, zsrc + p.N, zs_bytes, bar);
                     }
                     wsrc += 4 * row_words;
                     zsrc += (size_t)zs_rows * p.N;
@@ -299,7 +303,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 const uint32_t* zsp = reinterpret_cast<const uint32_t*>(wst + Cfg::kWBytes + zs_row * 512) + quarter * 32 + r;
                 uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
                 uint32_t zsw[4] = {0, 0, 0, 0};
-                if (has_tile) {
+                // a missing second half (K % 128 == 64) dequantises to zeros: codes 0 with zero point and scale 0
+                if (has_tile && !(dgroup == 1 && k_tail && ks == k_steps - 1)) {
                     q0 = wq[quarter * 32 + lane]; q1 = wq[128 + quarter * 32 + lane];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) zsw[j] = zsp[8 * j];
@@ -420,26 +425,32 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 if (*last_flag) {
                     __threadfence();
                     if (n_ok) {
+                        // 32 tokens per batch: part 0, then one part at a time added to it (fixed order, up to 32
+                        // loads in flight per thread - the reduction is a chain of L2 round trips otherwise)
                         const int c_last = min(c_end, p.tokens - tok0);      // ragged tile: stop at the last token
 #pragma unroll 1
-                        for (int c = c_begin; c < c_last; c += 8) {
-                            float v[4][8];                                   // up to 4 parts x 8 tokens in flight
+                        for (int c = c_begin; c < c_last; c += 32) {
                             const float* src = p.partial + (size_t)(tok0 + c) * p.N + n;
-                            const bool whole = c + 8 <= c_last;
+                            const bool whole = c + 32 <= c_last;
+                            float sum[32];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q)
+                            for (int j = 0; j < 32; ++j) sum[j] = (whole || c + j < c_last) ? __ldcg(src + (size_t)j * p.N) : 0.f;
+                            for (int q = 1; q < p.split; ++q) {
+                                const float* sq = src + (size_t)q * p.tokens * p.N;
+                                float part[32];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    v[q][j] = (q < p.split && (whole || c + j < c_last)) ? __ldcg(src + ((size_t)q * p.tokens + j) * p.N) : 0.f;
+                                for (int j = 0; j < 32; ++j) part[j] = (whole || c + j < c_last) ? __ldcg(sq + (size_t)j * p.N) : 0.f;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) sum[j] += part[j];
+                            }
                             if (whole && plain) {
                                 __half* dst = p.out + (size_t)(tok0 + c) * p.N + n;
 #pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    dst[(size_t)j * p.N] = __hadd(__float2half_rn(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j]), bias);
+                                for (int j = 0; j < 32; ++j) dst[(size_t)j * p.N] = __hadd(__float2half_rn(sum[j]), bias);
                             } else {
 #pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    if (c + j < c_last) finish(((v[0][j] + v[1][j]) + v[2][j]) + v[3][j], tok0 + c + j);
+                                for (int j = 0; j < 32; ++j)
+                                    if (c + j < c_last) finish(sum[j], tok0 + c + j);
                             }
                         }
                     }
@@ -505,7 +516,7 @@ struct TcPlan { int tok, split; };
 TcPlan pick_plan(int tokens, int N, int K, bool allow_split, int force_split = 0)
 {
     const int n_blocks = (N + kBlockN - 1) / kBlockN;
-    const long long k_steps = K / kBlockK;
+    const long long k_steps = (K + kBlockK - 1) / kBlockK;
     TcPlan best = {256, 1};
     double best_cost = -1;
     const int cands[3] = {256, 128, 64};
@@ -558,7 +569,7 @@ void tc_force_config(int tile_tokens, int split_k) { g_force_tok = tile_tokens; 
 
 bool tc_supported(int tokens, int N, int K, int g)
 {
-    return tokens > 0 && (g == 64 || g == 128) && (K % kBlockK) == 0 && (N % kTileN) == 0;
+    return tokens > 0 && (g == 64 || g == 128) && (K % 64) == 0 && (N % kTileN) == 0;
 }
 
 size_t tc_workspace_bytes(int tokens, int N, int K, int g)
@@ -649,7 +660,7 @@ extern "C" int w4a16_gemm_static_scratch(const void* x, const void* qweight, con
 {
     using namespace w4a16;
     if (group_size != 64 && group_size != 128) return W4A16_ERR_GROUP_SIZE;
-    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || (K % 128) || K < 1024) return W4A16_ERR_BAD_SHAPE;
+    if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || K < 1024) return W4A16_ERR_BAD_SHAPE;
     if (!x || !qweight || !zeros_scales || !out) return W4A16_ERR_NULL_POINTER;
     if (((uintptr_t)x & 15) || ((uintptr_t)qweight & 15) || ((uintptr_t)zeros_scales & 15) || ((uintptr_t)out & 15))
         return W4A16_ERR_MISALIGNED;
