@@ -306,7 +306,9 @@ int w4a16_debug_tmem_layout(void* out, void* stream);
 
 /* Debug aid (library built with -DW4A16_SKINNY_DEBUG): device buffer of uint64 [CTAs][16 warps][8] that receives
  * %globaltimer stamps of the decode kernels' phases; NULL switches it off.  8-token kernel: start, previous grid
- * complete, first unit landed, main loop done, partial sums visible, end. */
+ * complete, first unit landed, main loop done, partial sums visible, end.  The tcgen05 kernel writes to the same
+ * buffer the cycle accounting of CTA 0's MMA warp: int64 [7] = total cycles, cycles waiting for the dequantised A
+ * slot, for the activation stage, for the accumulator, stages whose A / activation probe missed, stages. */
 void w4a16_debug_skinny_timeline(void* buf);
 
 /* Benchmark/tuning hooks, not part of the drop-in surface (0 = automatic choice):

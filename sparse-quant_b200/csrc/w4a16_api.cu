@@ -88,6 +88,7 @@ void decode_force_kernel(int which);
 int gemv_plan(int tokens, int N, int K, int g, int* plan);
 void gemv_force_ahead(int units);
 void tc_force_config(int tile_tokens, int split_k);
+void tc_set_account(unsigned long long* buf);
 
 namespace {
 
@@ -285,6 +286,7 @@ extern "C" void w4a16_debug_skinny_timeline(void* buf)
 {
     skinny_set_timeline((unsigned long long*)buf);
     gemv_set_timeline((unsigned long long*)buf);
+    tc_set_account((unsigned long long*)buf);
 }
 extern "C" void w4a16_tune_tc(int tile_tokens, int split_k) { tc_force_config(tile_tokens, split_k); }
 // 1: the small decode-step kernels (attention, add+norm, SwiGLU product, exchange all-gather) are launched with

@@ -92,6 +92,7 @@ struct TcParams {
     int split;                      // K parts per output tile (1 = no split)
     float* partial;                 // split > 1: fp32 partial tiles [split][tokens][N]
     int*   counters;                // split > 1: arrivals per output tile (zero on entry, reset by the last arriver)
+    long long* account;             // debug builds: cycle accounting of CTA 0's MMA warp (8 words), or null
 };
 
 template <int TOK>
@@ -233,16 +234,38 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         // two barriers are therefore probed before this stage's MMAs; in steady state both are complete (every other
         // role runs ahead of the MMA) and the next iteration starts issuing at once.
         bool ready = false;
+#ifdef W4A16_SKINNY_DEBUG
+        // where this warp's cycles go: [0] total, [1] waiting for the A slot, [2] for the x stage, [3] for the
+        // accumulator, [4] / [5] stages whose A / x probe missed, [6] stages
+        long long acct[7] = {0, 0, 0, 0, 0, 0, 0};
+        const long long t_begin = clock64();
+#define TC_ACCT(i, v) acct[i] += (v)
+#else
+#define TC_ACCT(i, v)
+#endif
         for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+#ifdef W4A16_SKINNY_DEBUG
+            const long long cd0 = clock64();
+#endif
             ok = __all_sync(0xffffffffu, mbar_wait(dempty_bar, dphase ^ 1u, abort_flag, kWaitBudgetNs));   // epilogue drained D
             if (!ok) break;
+            TC_ACCT(3, clock64() - cd0);
             tc_fence_after_sync();
             int ks0, ks1;
             k_range(item, ks0, ks1);
             for (int ks = ks0; ks < ks1; ++ks) {
+                TC_ACCT(6, 1);
                 if (!ready) {
+#ifdef W4A16_SKINNY_DEBUG
+                    const long long c0 = clock64();
+                    ok = __all_sync(0xffffffffu, mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs));
+                    const long long c1 = clock64();
+                    ok = ok && __all_sync(0xffffffffu, mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs));
+                    acct[1] += c1 - c0; acct[2] += clock64() - c1;
+#else
                     ok = __all_sync(0xffffffffu, mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs) &&
                                                  mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs));
+#endif
                     if (!ok) break;
                 }
                 tc_fence_after_sync();
@@ -261,12 +284,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 }
                 __syncwarp();
                 ready = __all_sync(0xffffffffu, next_a && next_x);
+#ifdef W4A16_SKINNY_DEBUG
+                if (!__all_sync(0xffffffffu, next_a)) acct[4] += 1;
+                if (!__all_sync(0xffffffffu, next_x)) acct[5] += 1;
+#endif
             }
             if (!ok) break;
             if (elect_one()) tc_commit(dfull_bar);
             __syncwarp();
             dphase ^= 1u;
         }
+#ifdef W4A16_SKINNY_DEBUG
+        if (p.account && blockIdx.x == 0 && lane == 0) {
+            acct[0] = clock64() - t_begin;
+            for (int i = 0; i < 7; ++i) p.account[i] = acct[i];
+        }
+#endif
     } else {
         // ------------------------------ dequant + epilogue (warps 0..3 and 6..9) ------------------------------
         // Two groups of four warps; a warp may only touch the TMEM lane quarter (warp index % 4), which is also the
@@ -506,6 +539,7 @@ __global__ void __launch_bounds__(128, 1) tmem_layout_probe_kernel(uint32_t* out
 }
 
 int g_force_tok = 0, g_force_split = 0;
+long long* g_tc_account = nullptr;
 
 struct TcPlan { int tok, split; };
 
@@ -566,6 +600,7 @@ int launch_tok(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t
 }  // namespace
 
 void tc_force_config(int tile_tokens, int split_k) { g_force_tok = tile_tokens; g_force_split = split_k; }
+void tc_set_account(unsigned long long* buf) { g_tc_account = reinterpret_cast<long long*>(buf); }
 
 bool tc_supported(int tokens, int N, int K, int g)
 {
@@ -599,7 +634,7 @@ int launch_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaSt
 
     TcParams p;
     p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out; p.error = err;
-    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.g = a.g; p.relu = a.relu ? 1 : 0; p.residual = a.residual;
+    p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.g = a.g; p.relu = a.relu ? 1 : 0; p.residual = a.residual; p.account = g_tc_account;
     p.n_blocks = (a.N + kBlockN - 1) / kBlockN;
     p.t_blocks = (a.tokens + tok - 1) / tok;
     const long long tiles = (long long)p.n_blocks * p.t_blocks;
