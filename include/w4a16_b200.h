@@ -215,6 +215,13 @@ int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_s
                          void* out, int tokens, int N, int K, int group_size, int k_config,
                          void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
                          unsigned flags);
+/* The same with `residual` (fp16 [tokens, N], the same values on every rank, or NULL) added once to the summed
+ * output after bias / ReLU: the residual add that follows a row-parallel out_proj / fc2.  row_stats_out != NULL
+ * (tokens <= 16): the row statistics of the output for w4a16_gemm_prenorm, see there. */
+int w4a16_gemm_allreduce_residual(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                  const void* residual, void* out, void* row_stats_out, int tokens, int N, int K,
+                                  int group_size, int k_config, void* const* buffers, int world, int rank,
+                                  size_t capacity_elems, void* stream, unsigned flags);
 
 /*
  * Decode attention over a static key/value cache: one new token per sequence, one launch.  Replaces, for the
@@ -257,6 +264,34 @@ int w4a16_add_norm(const void* x, const void* delta, void* x_out, void* h_out, c
  * (act_fn(gate_proj(x)) * up_proj(x), modeling_llama_ours.py:272) on the output [rows, 2n] of the gate/up projections
  * fused into one GEMV; fp16, n % 8 == 0. */
 int w4a16_silu_mul(const void* gate_up, void* out, int rows, int n, void* stream);
+
+/*
+ * Normalisation folded into the decode GEMV that consumes it, residual add into the GEMV that produces the block
+ * output: two launches fewer per decoder layer.  The reference runs `hidden = residual + hidden` and LayerNorm /
+ * LlamaRMSNorm as torch kernels around q/k/v and fc1 / gate-up (modeling_opt_ours.py:561-562,590,603-604,614;
+ * modeling_llama_ours.py:113-118).  Here
+ *   w4a16_gemm_residual_stats  (and w4a16_gemm_allreduce_residual with row_stats_out != NULL):
+ *       out = linear(x) + residual, and per CTA of the grid the sum and the sum of squares of its slice of every
+ *       output row are left in `row_stats_out` (w4a16_row_stats_bytes(N) bytes, 16-byte aligned);
+ *   w4a16_gemm_prenorm:
+ *       out = linear(norm(x)) where x is that output and `row_stats` that buffer: the consumer adds the parts of a
+ *       row in index order (deterministic), mean = sum / K, variance = sum of squares / K - mean^2 in fp32, and
+ *       normalises its staged activations in place before the main loop.
+ *       rms == 0: LayerNorm(x) * norm_weight + norm_bias (norm_bias may be NULL), affine in fp32, one rounding to
+ *       fp16; rms != 0: norm_weight * fp16(x * rsqrt(mean(x^2) + eps)) - the arithmetic of w4a16_add_norm except for
+ *       the one-pass variance.  norm_weight / norm_bias fp16 [K], 16-byte aligned.
+ * Both need tokens <= 16 (one pass of the one-CTA-per-SM decode kernel), w4a16_gemm_prenorm also K <= 8192;
+ * W4A16_ERR_BAD_ALGO beyond that: call
+ * w4a16_add_norm and w4a16_gemm_fused instead.  flags as for w4a16_gemm_fused (no W4A16_FLAG_SILU_MUL for the
+ * producers).
+ */
+size_t w4a16_row_stats_bytes(int N);
+int w4a16_gemm_residual_stats(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                              const void* residual, void* out, void* row_stats_out, int tokens, int N, int K,
+                              int group_size, void* stream, unsigned flags);
+int w4a16_gemm_prenorm(const void* x, const void* row_stats, const void* norm_weight, const void* norm_bias, float eps,
+                       int rms, const void* qweight, const void* zeros_scales, const void* bias, void* out, int tokens,
+                       int N, int K, int group_size, void* stream, unsigned flags);
 
 /*
  * No counterpart in the reference.  The tcgen05 GEMM with K split in two, for callers that cannot

@@ -186,6 +186,59 @@ extern "C" int w4a16_gemm_fused(const void* x, const void* qweight, const void* 
     return launch_skinny(a, (cudaStream_t)stream);
 }
 
+extern "C" size_t w4a16_row_stats_bytes(int N)
+{
+    // header + one part per CTA of the producing grid (at most one per 32 out-features and K split) x 16 rows x 2 floats
+    return N <= 0 ? 0 : (size_t)(4 + (size_t)((N + 31) / 32) * 8 * 16 * 2) * sizeof(float);
+}
+
+extern "C" int w4a16_gemm_prenorm(const void* x, const void* row_stats, const void* norm_weight, const void* norm_bias,
+                                  float eps, int rms, const void* qweight, const void* zeros_scales, const void* bias,
+                                  void* out, int tokens, int N, int K, int group_size, void* stream, unsigned flags)
+{
+    int s = validate(x, qweight, zeros_scales, out, tokens, N, K, group_size);
+    if (s != W4A16_OK) return s;
+    if (!norm_weight || !row_stats) return W4A16_ERR_NULL_POINTER;
+    if (((uintptr_t)norm_weight & 15) || ((uintptr_t)norm_bias & 15) || ((uintptr_t)row_stats & 15)) return W4A16_ERR_MISALIGNED;
+    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU | W4A16_FLAG_SILU_MUL)) return W4A16_ERR_BAD_ALGO;
+    if ((flags & W4A16_FLAG_SILU_MUL) && (N % 64)) return W4A16_ERR_BAD_ALGO;
+    if (tokens == 0) return W4A16_OK;
+    s = check_device();
+    if (s != W4A16_OK) return s;
+    GemmArgs a;
+    a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
+    a.bias = (const __half*)bias; a.out = (__half*)out;
+    a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
+    a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
+    a.relu = (flags & W4A16_FLAG_RELU) != 0;
+    a.silu_mul = (flags & W4A16_FLAG_SILU_MUL) != 0;
+    a.norm_weight = (const __half*)norm_weight; a.norm_bias = (const __half*)norm_bias; a.norm_eps = eps; a.norm_rms = rms != 0;
+    a.row_stats_in = (const float*)row_stats;
+    return launch_skinny(a, (cudaStream_t)stream);       // W4A16_ERR_BAD_ALGO beyond 16 tokens
+}
+
+extern "C" int w4a16_gemm_residual_stats(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                         const void* residual, void* out, void* row_stats_out, int tokens, int N, int K,
+                                         int group_size, void* stream, unsigned flags)
+{
+    int s = validate(x, qweight, zeros_scales, out, tokens, N, K, group_size);
+    if (s != W4A16_OK) return s;
+    if (!row_stats_out) return W4A16_ERR_NULL_POINTER;
+    if (((uintptr_t)row_stats_out & 15) || ((uintptr_t)residual & 1)) return W4A16_ERR_MISALIGNED;
+    if (flags & ~(unsigned)(W4A16_FLAG_STATIC_WEIGHTS | W4A16_FLAG_RELU)) return W4A16_ERR_BAD_ALGO;
+    if (tokens == 0) return W4A16_OK;
+    s = check_device();
+    if (s != W4A16_OK) return s;
+    GemmArgs a;
+    a.x = (const __half*)x; a.qw = (const uint32_t*)qweight; a.zs = (const uint32_t*)zeros_scales;
+    a.bias = (const __half*)bias; a.out = (__half*)out; a.residual = (const __half*)residual;
+    a.tokens = tokens; a.N = N; a.K = K; a.g = group_size;
+    a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
+    a.relu = (flags & W4A16_FLAG_RELU) != 0;
+    a.row_stats_out = (float*)row_stats_out;
+    return launch_skinny(a, (cudaStream_t)stream);       // W4A16_ERR_BAD_ALGO beyond 16 tokens
+}
+
 extern "C" int w4a16_gemm_ex(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
                              void* out, int tokens, int N, int K, int group_size, void* workspace,
                              size_t workspace_bytes, void* stream, int algo, unsigned flags)

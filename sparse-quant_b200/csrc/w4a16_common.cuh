@@ -166,6 +166,15 @@ struct GemmArgs {
     bool silu_mul = false; // W4A16_FLAG_SILU_MUL: gate / up tiles alternate, out = silu(gate) * up, [tokens, N / 2] (decode kernels)
     const __half* residual = nullptr;   // [tokens, N] added after bias / ReLU, or null
     const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
+    // non-null: x is normalised row by row (LayerNorm, or RMSNorm when norm_rms) after it is staged - the launch of
+    // the normalisation kernel in front of the GEMV is saved (<= 16 tokens, one-CTA-per-SM decode kernel only).  The
+    // row statistics come from the GEMV that produced x (row_stats_in = its row_stats_out).
+    const float* row_stats_in = nullptr;
+    float* row_stats_out = nullptr;       // non-null: row statistics of this call's output for the next GEMV
+    const __half* norm_weight = nullptr;
+    const __half* norm_bias = nullptr;    // LayerNorm only, may be null
+    float norm_eps = 0.f;
+    bool norm_rms = false;
 };
 
 // Launch, optionally with programmatic stream serialization (the grid may then be scheduled while the previous

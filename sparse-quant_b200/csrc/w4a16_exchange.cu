@@ -172,11 +172,12 @@ extern "C" void w4a16_tune_exchange_wait(unsigned milliseconds)
     g_peer_wait_ns.store(milliseconds ? (unsigned long long)milliseconds * 1000000ull : 2000ull * 1000 * 1000, std::memory_order_relaxed);
 }
 
-extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
-                                    void* out, int tokens, int N, int K, int group_size, int k_config,
-                                    void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
-                                    unsigned flags)
+extern "C" int w4a16_gemm_allreduce_residual(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                             const void* residual, void* out, void* row_stats_out, int tokens, int N, int K,
+                                             int group_size, int k_config, void* const* buffers, int world, int rank,
+                                             size_t capacity_elems, void* stream, unsigned flags)
 {
+    if ((residual && ((uintptr_t)residual & 1)) || ((uintptr_t)row_stats_out & 15)) return W4A16_ERR_MISALIGNED;
     if (group_size != 32 && group_size != 64 && group_size != 128) return W4A16_ERR_GROUP_SIZE;
     if (tokens <= 0 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || k_config < K) return W4A16_ERR_BAD_SHAPE;
     if (tokens > 32) return W4A16_ERR_TOO_LARGE;
@@ -201,7 +202,18 @@ extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const vo
     a.static_weights = (flags & W4A16_FLAG_STATIC_WEIGHTS) != 0;
     a.relu = (flags & W4A16_FLAG_RELU) != 0;
     a.exchange = &ex;
+    a.residual = (const __half*)residual;
+    a.row_stats_out = (float*)row_stats_out;
     return launch_skinny(a, (cudaStream_t)stream);
+}
+
+extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
+                                    void* out, int tokens, int N, int K, int group_size, int k_config,
+                                    void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,
+                                    unsigned flags)
+{
+    return w4a16_gemm_allreduce_residual(x, qweight, zeros_scales, bias, nullptr, out, nullptr, tokens, N, K, group_size, k_config,
+                                         buffers, world, rank, capacity_elems, stream, flags);
 }
 
 extern "C" int w4a16_exchange_allgather(const void* in, void* out, int words, void* const* buffers, int world, int rank,

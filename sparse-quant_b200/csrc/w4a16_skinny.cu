@@ -83,6 +83,12 @@ struct SkinnyParams {
     int depth;       // units in flight per warp (>= 2)
     int warps;       // warps per CTA
     const __half* residual;   // [tokens, N] added to the output after bias / ReLU (fp16 add), or null
+    const __half* norm_w;     // non-null: x rows are normalised after they are staged (weight [K]); needs stats_in
+    const float* stats_in;    // row statistics of x written by the GEMV that produced it
+    float* stats_out;         // non-null: row statistics of this call's output (after bias / ReLU / residual) are written here
+    const __half* norm_b;     // LayerNorm bias [K] or null
+    float norm_eps;
+    int norm_rms;             // 1: RMSNorm (weight * fp16(x * rstd)), 0: LayerNorm
     int silu_mul;    // out-feature tiles alternate gate / up; out[t, j] = silu(gate_j) * up_j, [tokens, N / 2]
     int relu;        // clamp the outputs at zero after the bias add
     int pdl;         // 1: launched with programmatic stream serialization; weights may be fetched before the previous grid ends
@@ -220,8 +226,15 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
     return v;
 }
 
+// Row statistics handed from a GEMV to the next one (device buffer of floats): [0] = number of parts (int bits),
+// [1..3] unused, then per part 16 rows x (sum, sum of squares) of the part's slice of the output row.  A part is one
+// CTA of the producing grid; the consumer adds the parts of a row in index order.
+constexpr int kStatsHeaderFloats = 4;
+constexpr int kStatsRows = 16;
+constexpr int kStatsOffset = 1088;             // byte offset in the shared-memory header of 32 floats of scratch
+
 // TG = token groups of 8 handled per pass (1, 2, 4); G = quantisation group size.
-template <int TG, int G, int kWarps>
+template <int TG, int G, int kWarps, bool kPreNorm = false>
 __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParams p)
 {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -303,6 +316,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         }
     };
 
+    constexpr bool prenorm = kPreNorm;                          // its own instantiation: the plain kernel keeps its registers
+    // Fused normalisation: thread t owns the 16-byte column vectors c = t % nv (+ nv_step) of the staged K range and the
+    // token rows t / nv, t / nv + kThreads / nv, ...  The affine parameters of its columns are static like the packed
+    // weights: they are fetched before the wait for the previous kernel, so that no global load sits between the
+    // arrival of the activations and the main loop.
+    const int pn_nv = copy_halfs >> 3;                          // vectors of the staged range per row
+    const int pn_cols = pn_nv < kThreads ? pn_nv : kThreads;    // distinct first columns among the threads
+    const int pn_c0 = pn_cols > 0 ? (int)threadIdx.x % pn_cols : 0, pn_r0 = pn_cols > 0 ? (int)threadIdx.x / pn_cols : 0;
+    const int pn_rstep = pn_cols > 0 ? kThreads / pn_cols : 1;  // rows advance by this much (0 rows left over when nv > kThreads)
+    uint4 pn_w[2], pn_b[2];
+    if constexpr (prenorm) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c = pn_c0 + j * kThreads;
+            pn_w[j] = make_uint4(0, 0, 0, 0);
+            pn_b[j] = make_uint4(0, 0, 0, 0);
+            if (c < pn_nv) {
+                pn_w[j] = *reinterpret_cast<const uint4*>(p.norm_w + kc0 + c * 8);
+                if (p.norm_b) pn_b[j] = *reinterpret_cast<const uint4*>(p.norm_b + kc0 + c * 8);
+            }
+        }
+    }
     if (p.pdl) {
         // Programmatic dependent launch: this grid may start while the previous kernel of the stream is
         // still draining.  The packed weights are static by contract, so their copies start at once; the
@@ -325,7 +360,64 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         }
     }
     __syncthreads();                                            // barrier initialised, zero tail written
-    if (stage_x) mbar_wait(xbar, 0, abort_flag, kWaitBudgetNs);
+    if constexpr (prenorm) {
+        // Normalisation folded into this GEMV (the launch of the normalisation kernel in front of it is saved): the
+        // row statistics come from the GEMV that produced x (its CTAs each left the sum and the sum of squares of
+        // their slice of every row); warp r adds the parts of row r in index order while the activation copies are
+        // in flight, then the staged K range is normalised in place.
+        static_assert(32 + kMaxWarps * kMaxDepth * 8 <= kStatsOffset && kStatsOffset + 2 * kStatsRows * 4 <= kHeaderBytes, "scratch in the header");
+        float* mean_s = reinterpret_cast<float*>(smem + kStatsOffset);
+        float* rstd_s = mean_s + kStatsRows;
+        if (warp < rows) {
+            const int parts = *reinterpret_cast<const int*>(p.stats_in);
+            const float2* data = reinterpret_cast<const float2*>(p.stats_in + kStatsHeaderFloats) + tok0 + warp;
+            float a = 0.f, b = 0.f;
+            for (int i = lane; i < parts; i += 32) {
+                const float2 v = data[(size_t)i * kStatsRows];
+                a += v.x;
+                b += v.y;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                b += __shfl_xor_sync(0xffffffffu, b, o);
+            }
+            if (lane == 0) {
+                const float mean = p.norm_rms ? 0.f : a / p.K;
+                const float var = fmaxf(b / p.K - mean * mean, 0.f);
+                mean_s[warp] = mean;
+                rstd_s[warp] = rsqrtf(var + p.norm_eps);
+            }
+        }
+        if (stage_x) mbar_wait(xbar, 0, abort_flag, kWaitBudgetNs);
+        __syncthreads();                                        // statistics visible to every thread
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c = pn_c0 + j * kThreads;
+            if (c < pn_nv) {
+                const __half* wh = reinterpret_cast<const __half*>(&pn_w[j]);
+                const __half* bh = reinterpret_cast<const __half*>(&pn_b[j]);
+                for (int row = pn_r0 < pn_rstep ? pn_r0 : rows; row < rows; row += pn_rstep) {   // threads beyond the last full group idle
+                    __half* px = xs + row * p.xs_stride + c * 8;
+                    const uint4 xv = *reinterpret_cast<const uint4*>(px);
+                    const __half* xh = reinterpret_cast<const __half*>(&xv);
+                    const float m = mean_s[row], rs = rstd_s[row];
+                    uint4 o;
+                    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float f = __half2float(xh[e]);
+                        if (p.norm_rms) oh[e] = __hmul(wh[e], __float2half_rn(f * rs));
+                        else oh[e] = __float2half_rn((f - m) * rs * __half2float(wh[e]) + __half2float(bh[e]));
+                    }
+                    *reinterpret_cast<uint4*>(px) = o;
+                }
+            }
+        }
+        __syncthreads();                                        // normalised activations visible to every warp
+    } else {
+        if (stage_x) mbar_wait(xbar, 0, abort_flag, kWaitBudgetNs);
+    }
     if (tl) tl[1] = globaltimer_ns();
 
     // sum_k x[t, k] per quantisation group, by an MMA with an all-ones A fragment over the staged activations (every
@@ -477,6 +569,24 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
     };
     const int Er = p.silu_mul ? rows << (nloc_shift - 1) : rows << nloc_shift;
     const int e_lo = div_splits(Er * rank), e_hi = div_splits(Er * (rank + 1));
+    // Which outputs a thread finalises.  Default: the rank's flat slice of the (token, out-feature) space dealt over the
+    // threads.  With row statistics requested a warp stays inside ONE token row (token = warp % Rp, the row's columns
+    // of this rank dealt over the kWarps / Rp warps of the row), so that the sums of a row are per-thread accumulators
+    // added in a fixed order.  Both passes of the fused exchange walk the same elements.
+    const bool by_row = p.stats_out != nullptr;
+    const int rp_shift = rows <= 1 ? 0 : 32 - __clz(rows - 1);                   // Rp = 2^rp_shift >= rows (rows <= kWarps)
+    const int row_tok = warp & ((1 << rp_shift) - 1), row_sub = warp >> rp_shift, row_nsub = max(kWarps >> rp_shift, 1);
+    const int col_lo = div_splits(nloc * rank), col_hi = div_splits(nloc * (rank + 1));
+    const int row_nl0 = col_lo + ((col_hi - col_lo) * row_sub) / row_nsub, row_nl1 = col_lo + ((col_hi - col_lo) * (row_sub + 1)) / row_nsub;
+    float st1 = 0.f, st2 = 0.f;                                                  // sum and sum of squares of this thread's outputs
+    auto for_each = [&](auto&& body) {
+        if (by_row) {
+            if (row_tok < rows)
+                for (int nl = row_nl0 + lane; nl < row_nl1; nl += 32) body(row_tok, nl);
+        } else {
+            for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) body(e >> nloc_shift, e & (nloc - 1));
+        }
+    };
     if (p.silu_mul) {
         // SwiGLU epilogue: the out-feature tiles alternate gate, up, gate, up ... (fused that way at load time), so
         // local out-features nl and nl + 32 are a (gate, up) pair of the same hidden unit and one thread owns both:
@@ -495,8 +605,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             }
         }
     } else {
-        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
-            const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+        for_each([&](int tok, int nl) {
             const float s = total(tok, nl);
             const int n = blockIdx.x * nloc + nl;
             if (n < p.N) {
@@ -511,9 +620,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                     const size_t idx = (size_t)(tok0 + tok) * p.N + n;
                     if (p.residual) h = __hadd(h, p.residual[idx]);
                     p.out[idx] = h;
+                    const float hv = __half2float(h);
+                    st1 += hv;
+                    st2 += hv * hv;
                 }
             }
-        }
+        });
     }
     if (S > 1) cluster.sync();                              // peers may still be reading this CTA's partials
     if (fused) {
@@ -525,10 +637,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         // once a wait has given up the buffer stays marked and later calls do not wait at all: the job is lost
         // either way and must not take seconds per call to find out
         bool dead = *reinterpret_cast<volatile int*>(&hdr->error) != 0;
-        for (int e = e_lo + threadIdx.x; e < e_hi; e += kThreads) {
-            const int tok = e >> nloc_shift, nl = e & (nloc - 1);
+        for_each([&](int tok, int nl) {
             const int n = blockIdx.x * nloc + nl;
-            if (n >= p.N) continue;
+            if (n >= p.N) return;
             const size_t idx = (size_t)(tok0 + tok) * p.N + n;
             uint2 v[kExchangeMaxWorld];
             uint64_t t0 = 0;
@@ -562,7 +673,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             __half h = finish(s, n);
             if (p.residual) h = __hadd(h, p.residual[idx]);
             p.out[idx] = h;
-        }
+            const float hv = __half2float(h);
+            st1 += hv;
+            st2 += hv * hv;
+        });
         __syncthreads();
         // the last CTA to get here advances the epoch; the next call then uses the other half of the buffers
         if (threadIdx.x == 0) {
@@ -573,6 +687,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
                 *reinterpret_cast<volatile unsigned*>(&hdr->epoch) = epoch + 1;
             }
         }
+    }
+    if (by_row) {
+        // row statistics of this CTA's outputs: lanes, then the warps of a row in index order, then one store per row
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            st1 += __shfl_xor_sync(0xffffffffu, st1, o);
+            st2 += __shfl_xor_sync(0xffffffffu, st2, o);
+        }
+        float2* red = reinterpret_cast<float2*>(smem + kStatsOffset);            // [kWarps]
+        if (lane == 0) red[warp] = make_float2(st1, st2);
+        __syncthreads();
+        if ((int)threadIdx.x < rows) {
+            float a = 0.f, b = 0.f;
+            for (int sub = 0; sub < row_nsub; ++sub) {
+                const float2 v = red[(sub << rp_shift) + threadIdx.x];
+                a += v.x;
+                b += v.y;
+            }
+            const int part = blockIdx.x * S + rank;
+            reinterpret_cast<float2*>(p.stats_out + kStatsHeaderFloats)[(size_t)part * kStatsRows + tok0 + threadIdx.x] = make_float2(a, b);
+        }
+        if (threadIdx.x == 0 && blockIdx.x == 0 && rank == 0) *reinterpret_cast<int*>(p.stats_out) = (int)gridDim.x * S;
     }
     if (tl) tl[7] = globaltimer_ns();
 }
@@ -591,7 +727,8 @@ int xs_bytes(int rows, int K, int splits, int kUnitK)
 {
     const int units = (K + kUnitK - 1) / kUnitK;
     const int cta_units = (units + splits - 1) / splits;
-    return (int)(((size_t)rows * (cta_units * kUnitK + 8) * sizeof(__half) + 127) / 128 * 128);
+    const int bytes = (int)(((size_t)rows * (cta_units * kUnitK + 8) * sizeof(__half) + 127) / 128 * 128);
+    return bytes < 1152 ? 1152 : bytes;                 // the fused normalisation uses the area as reduction scratch first
 }
 
 int xsum_bytes(int tg, int K, int splits, int kUnitK, int g)
@@ -697,7 +834,7 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4, int min_wn =
     return c;
 }
 
-template <int TG, int G, int kWarps>
+template <int TG, int G, int kWarps, bool kPreNorm = false>
 int launch_instance(const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, size_t smem, cudaStream_t st)
 {
     static int configured_dev[64] = {0};   // benign race: the attribute call is idempotent
@@ -713,7 +850,7 @@ int launch_instance(const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, s
     }
     if (dev < 64 && (int)smem > max_optin[dev]) return W4A16_ERR_BAD_SHAPE;
     if (dev >= 64 || configured_dev[dev] < (int)smem) {
-        e = cudaFuncSetAttribute(skinny_kernel<TG, G, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(skinny_kernel<TG, G, kWarps, kPreNorm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev < 64) configured_dev[dev] = (int)smem;
     }
@@ -731,7 +868,7 @@ int launch_instance(const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, s
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.pdl ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, skinny_kernel<TG, G, kWarps>, wmap, p);
+    e = cudaLaunchKernelEx(&cfg, skinny_kernel<TG, G, kWarps, kPreNorm>, wmap, p);
     count_launch();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
 }
@@ -740,6 +877,9 @@ template <int G>
 int launch_g(int tg, const CUtensorMap& wmap, const SkinnyParams& p, dim3 grid, size_t ring_bytes, cudaStream_t st)
 {
     const size_t smem = (size_t)p.ring_offset + ring_bytes;
+    if (p.norm_w) {                         // at most 16 tokens (checked by launch_skinny)
+        return tg == 1 ? launch_instance<1, G, 16, true>(wmap, p, grid, smem, st) : launch_instance<2, G, 16, true>(wmap, p, grid, smem, st);
+    }
     switch (tg) {
         case 1: return launch_instance<1, G, 16>(wmap, p, grid, smem, st);
         case 2: return launch_instance<2, G, 16>(wmap, p, grid, smem, st);
@@ -771,6 +911,13 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     // single-CTA kernel below, whose main loop issues fewer instructions per tile, wins on larger matrices and at 1..4
     // tokens.
     const bool small = (long long)a.K * a.N <= 20ll * 1000 * 1000;
+    if (a.norm_weight || a.row_stats_out) {
+        // normalisation folded into the GEMV / row statistics for the next one: one pass of at most 16 tokens in
+        // the one-CTA-per-SM kernel
+        if (a.tokens > 16 || (a.K % 8) || a.silu_mul && a.row_stats_out) return W4A16_ERR_BAD_ALGO;
+        if (a.norm_weight && !a.row_stats_in) return W4A16_ERR_NULL_POINTER;
+        if (a.norm_weight && a.K > 2 * 512 * 8) return W4A16_ERR_BAD_ALGO;   // two column vectors per thread
+    } else
     if (g_decode_kernel == 2 || (g_decode_kernel == 0 && a.tokens >= 5 && a.tokens <= 8 && small)) return launch_gemv(a, st);
     // with the fused exchange every rank must launch the same shape: choose it from the K all ranks agreed on
     const int k_config = a.exchange ? a.exchange->k_config : a.K;
@@ -813,6 +960,8 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     p.inv_splits = c.splits > 1 ? (unsigned)(((1ull << 32) + c.splits - 1) / c.splits) : 0u;
     p.tokens = a.tokens; p.N = a.N; p.K = a.K; p.wn = c.wn; p.splits = c.splits; p.debug_mode = g_debug_mode; p.timeline = g_timeline; p.depth = c.depth; p.warps = c.warps; p.pdl = a.static_weights ? 1 : 0; p.relu = a.relu ? 1 : 0;
     p.residual = a.residual; p.silu_mul = a.silu_mul ? 1 : 0;
+    p.norm_w = a.norm_weight; p.norm_b = a.norm_bias; p.norm_eps = a.norm_eps; p.norm_rms = a.norm_rms ? 1 : 0;
+    p.stats_in = a.row_stats_in; p.stats_out = a.row_stats_out;
     const int max_cta_units = (units + c.splits - 1) / c.splits;
     p.xs_stride = max_cta_units * kUnitK + 8;           // +16 B: ldmatrix rows fall in distinct banks
     const int tok = 8 * c.tg;
@@ -823,6 +972,7 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
     if (a.exchange && grid.z != 1) return W4A16_ERR_TOO_LARGE;
+    if ((a.norm_weight || a.row_stats_out) && grid.z != 1) return W4A16_ERR_BAD_ALGO;
     // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words
     CUtensorMap wmap;
     {

@@ -39,6 +39,9 @@ C_ABI = {
     "w4a16_gemm_algo": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci]),
     "w4a16_gemm_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
     "w4a16_gemm_fused": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, _sz, _vp, _ci, ctypes.c_uint]),
+    "w4a16_gemm_prenorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _ci, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, ctypes.c_uint]),
+    "w4a16_gemm_residual_stats": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _vp, ctypes.c_uint]),
+    "w4a16_row_stats_bytes": (_sz, [_ci]),
     "w4a16_workspace_bytes": (_sz, [_ci, _ci, _ci, _ci]),
     "w4a16_exchange_bytes": (_sz, [_ci, _sz]),
     "w4a16_exchange_alloc": (_ci, [_ci, _sz, ctypes.POINTER(_vp)]),
@@ -50,6 +53,8 @@ C_ABI = {
     "w4a16_exchange_allgather": (_ci, [_vp, _vp, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz, _vp]),
     "w4a16_gemm_allreduce": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz,
                                    _vp, ctypes.c_uint]),
+    "w4a16_gemm_allreduce_residual": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci,
+                                            _ci, _sz, _vp, ctypes.c_uint]),
     "w4a16_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.c_float, _vp]),
     "w4a16_tune_attention": (None, [_ci]),
     "w4a16_tune_aux_launch": (None, [_ci]),
@@ -139,8 +144,24 @@ FLAG_RELU = 2
 FLAG_SILU_MUL = 4
 
 
+def prenorm_supported(tokens: int, K: int) -> bool:
+    """Whether w4a16_gemm_prenorm takes this input (see include/w4a16_b200.h)."""
+    return 0 < tokens <= 16 and K % 8 == 0 and K <= 8192
+
+
+def row_stats_supported(tokens: int) -> bool:
+    """Whether w4a16_gemm_residual_stats / w4a16_gemm_allreduce_residual write row statistics for this many tokens."""
+    return 0 < tokens <= 16
+
+
+def row_stats_buffer(N: int, device):
+    """A buffer for the row statistics a GEMV with N out-features leaves for the GEMV that normalises its output."""
+    return torch.zeros(load_library().w4a16_row_stats_bytes(int(N)) // 4, dtype=torch.float32, device=device)
+
+
 def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int = ALGO_AUTO, out=None,
-                  static_weights: bool = False, relu: bool = False, residual=None, silu_mul: bool = False):
+                  static_weights: bool = False, relu: bool = False, residual=None, silu_mul: bool = False,
+                  pre_norm=None, stats_out=None):
     """gemm_awq_ut with the fp16 bias add of WALinear.forward fused into the kernel epilogue.
 
     I fp16 [b, s, K] (CUDA, contiguous); W int32 [K, N/8] tile-ordered; W_zeros_scales fp16
@@ -150,6 +171,9 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
     relu=True passes W4A16_FLAG_RELU: max(., 0) applied after the bias add.
     residual (fp16 [b, s, N]) is added to the output in the kernel epilogue; silu_mul=True passes
     W4A16_FLAG_SILU_MUL (gate / up tiles interleaved, see w4a16_gemm_fused): returns fp16 [b, s, N/2].
+    pre_norm = (weight, bias or None, eps, rms, stats): the linear is applied to LayerNorm / RMSNorm of I; `stats` is the
+    row_stats_buffer the GEMV that produced I filled (stats_out=...), or None: the normalisation then runs as its own
+    launch.  stats_out: leave the row statistics of this call's output there (up to 16 tokens; ignored beyond).
     """
     _check_tensor(I, "I", dtype=torch.float16, dims=3)
     _check_tensor(W, "W", dims=2)
@@ -176,6 +200,36 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
         _need(tuple(out.shape) == (b, s, n_out) and out.device == I.device, "Tensor O must have shape [b, s, N]")
     lib = load_library()
     tokens = b * s
+    if pre_norm is not None:
+        # (weight, bias or None, eps, rms): I is the un-normalised input; the normalisation runs inside the decode
+        # kernel while it stages its activations (w4a16_gemm_prenorm), or as its own launch where that has no room
+        nw, nb, eps, rms, stats = pre_norm if len(pre_norm) == 5 else (*pre_norm, None)
+        _check_tensor(nw, "norm weight", dtype=torch.float16)
+        _need(nw.numel() == K and nw.device == I.device, "norm weight must have K elements on the same device")
+        if nb is not None:
+            _check_tensor(nb, "norm bias", dtype=torch.float16)
+            _need(nb.numel() == K and nb.device == I.device, "norm bias must have K elements on the same device")
+        if stats is not None and residual is None and algo == ALGO_AUTO and prenorm_supported(tokens, K):
+            with torch.cuda.device(I.device):
+                st = lib.w4a16_gemm_prenorm(I.data_ptr(), stats.data_ptr(), nw.data_ptr(),
+                                            nb.data_ptr() if (nb is not None and not rms) else None,
+                                            float(eps), int(bool(rms)), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                            bias.data_ptr() if bias is not None else None, out.data_ptr(), tokens, N, K,
+                                            group_size, _stream(I),
+                                            (FLAG_STATIC_WEIGHTS if static_weights else 0) | (FLAG_RELU if relu else 0) |
+                                            (FLAG_SILU_MUL if silu_mul else 0))
+            _check(st, "gemm_awq_ut")
+            return out
+        I = add_norm(I, None, nw, nb, eps, rms)[1]
+    if stats_out is not None and not silu_mul and algo == ALGO_AUTO and row_stats_supported(tokens):
+        with torch.cuda.device(I.device):
+            st = lib.w4a16_gemm_residual_stats(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                               bias.data_ptr() if bias is not None else None,
+                                               residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                               stats_out.data_ptr(), tokens, N, K, group_size, _stream(I),
+                                               (FLAG_STATIC_WEIGHTS if static_weights else 0) | (FLAG_RELU if relu else 0))
+        _check(st, "gemm_awq_ut")
+        return out
     with torch.cuda.device(I.device):
         ws_bytes = lib.w4a16_workspace_bytes(tokens, N, K, group_size)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=I.device) if ws_bytes else None
@@ -191,12 +245,13 @@ def gemm_awq_bias(I, W, W_zeros_scales, bias, N: int, group_size: int, algo: int
 
 
 def gemm_awq_allreduce(I, W, W_zeros_scales, bias, N: int, group_size: int, k_config: int, buffers, world: int,
-                       rank: int, capacity: int, out=None, static_weights: bool = False):
+                       rank: int, capacity: int, out=None, static_weights: bool = False, residual=None, stats_out=None):
     """Row-parallel linear for decode: this rank's K shard times its slice of the activations, summed over the
     ranks inside the kernel through peer memory (see w4a16_gemm_allreduce in include/w4a16_b200.h).
 
     I fp16 [b, s, K_shard] with b*s <= 32; `buffers` is a ctypes array of `world` device pointers (every rank's
     exchange buffer, own included); `bias` (N elements or None) must be the same on all ranks and is added once.
+    `residual` (fp16 [b, s, N], the same on all ranks, or None) is added once to the summed output.
     Returns fp16 [b, s, N], identical on every rank.
     """
     _check_tensor(I, "I", dtype=torch.float16, dims=3)
@@ -211,14 +266,19 @@ def gemm_awq_allreduce(I, W, W_zeros_scales, bias, N: int, group_size: int, k_co
     if bias is not None:
         _check_tensor(bias, "bias", dtype=torch.float16)
         _need(bias.numel() == N, "Tensor bias must have N elements")
+    if residual is not None:
+        _check_tensor(residual, "residual", dtype=torch.float16)
+        _need(residual.numel() == b * s * N and residual.device == I.device, "Tensor residual must have b*s*N elements")
     if out is None:
         out = torch.empty((b, s, N), dtype=torch.float16, device=I.device)
     lib = load_library()
     with torch.cuda.device(I.device):
-        st = lib.w4a16_gemm_allreduce(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
-                                      bias.data_ptr() if bias is not None else None, out.data_ptr(), b * s, N, K,
-                                      group_size, int(k_config), buffers, int(world), int(rank), int(capacity),
-                                      _stream(I), FLAG_STATIC_WEIGHTS if static_weights else 0)
+        st = lib.w4a16_gemm_allreduce_residual(I.data_ptr(), W.data_ptr(), W_zeros_scales.data_ptr(),
+                                               bias.data_ptr() if bias is not None else None,
+                                               residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                               stats_out.data_ptr() if (stats_out is not None and b * s <= 16) else None,
+                                               b * s, N, K, group_size, int(k_config), buffers, int(world), int(rank),
+                                               int(capacity), _stream(I), FLAG_STATIC_WEIGHTS if static_weights else 0)
     _check(st, "gemm_awq_allreduce")
     return out
 

@@ -43,6 +43,10 @@ class DecoderConfig:
     max_positions: int = 2048
     rope_theta: float = 10000.0
     rms_eps: float = 1e-6
+    # token step: normalisations folded into the GEMVs that consume them and residual adds into the GEMVs that produce
+    # the block outputs (5 launches per layer); False keeps them as separate add+norm launches (7 per layer)
+    fold_norms: bool = True
+    fold_norms_max_batch: int = 8
 
     @staticmethod
     def opt_6_7b():
@@ -175,27 +179,37 @@ def _norm_args(norm):
     return norm.weight, norm.bias, norm.eps, False
 
 
-def _layer_forward_static(self, x, delta, pos_t, rope):
+def _layer_forward_static(self, x, pos_t, rope, stats=None):
     """One-token step with the position held in a device tensor (fixed shapes: capturable in a CUDA graph).
-    `delta` is the previous block's output still to be added to the residual stream `x` (None for the first
-    layer): the add is fused with the normalisation that follows it.  The fused q/k/v GEMV feeds the decode
-    attention kernel, which also appends to the cache and applies the rotary embedding (`rope` = the full
-    (cos, sin) tables or None).  Returns (x, delta) for the next layer."""
+    `x` is the residual stream [B, 1, H].  With cfg.fold_norms and up to 16 sequences a layer is five launches: both
+    residual adds run in the epilogue of the GEMV that produces the block's output (after the cross-rank sum under
+    tensor parallelism), which also leaves the row statistics of the new residual stream; both normalisations run
+    inside the GEMV that consumes them, from those statistics.  `stats` = (buffer holding the statistics of x or None,
+    buffer for the attention block's output, buffer for this layer's output).  The fused q/k/v GEMV feeds the decode
+    attention kernel, which also appends to the cache and applies the rotary embedding (`rope` = the full (cos, sin)
+    tables or None).  Returns the new residual stream."""
     from quant import add_norm, decode_attention, silu_mul
     B, S, H = x.shape
-    x, h = add_norm(x, delta, *_norm_args(self.ln1))
-    qkv = self.qkv_proj(h).view(B, -1)
-    a = decode_attention(qkv, self.k_cache, self.v_cache, pos_t, self.local_heads, rope=rope).view(B, 1, -1)
-    x, h = add_norm(x, self.out_proj(a), *_norm_args(self.ln2))
-    if self.cfg.kind == "opt":
-        delta = self.fc2(self.fc1(h.reshape(1, B, H), relu=True)).reshape(B, 1, H)
-    else:
+    if stats is None:
+        _, h = add_norm(x, None, *_norm_args(self.ln1))
+        qkv = self.qkv_proj(h).view(B, -1)
+        a = decode_attention(qkv, self.k_cache, self.v_cache, pos_t, self.local_heads, rope=rope).view(B, 1, -1)
+        x, h = add_norm(x, self.out_proj(a), *_norm_args(self.ln2))
+        if self.cfg.kind == "opt":
+            return x + self.fc2(self.fc1(h.reshape(1, B, H), relu=True)).reshape(B, 1, H)
         if B <= 32:
-            delta = self.fc2(self.gate_up_proj(h, silu_mul=True))           # SwiGLU product in the GEMV epilogue
-        else:
-            gate, up = split_gate_up(self.gate_up_proj(h))
-            delta = self.fc2(silu_mul(torch.cat((gate, up), dim=-1)))
-    return x, delta
+            return x + self.fc2(self.gate_up_proj(h, silu_mul=True))
+        gate, up = split_gate_up(self.gate_up_proj(h))
+        return x + self.fc2(silu_mul(torch.cat((gate, up), dim=-1)))
+    s_in, s_mid, s_out = stats
+    qkv = self.qkv_proj(x, pre_norm=(*_norm_args(self.ln1), s_in)).view(B, -1)
+    a = decode_attention(qkv, self.k_cache, self.v_cache, pos_t, self.local_heads, rope=rope).view(B, 1, -1)
+    x = self.out_proj(a, residual=x, stats_out=s_mid)
+    ln2 = (*_norm_args(self.ln2), s_mid)
+    if self.cfg.kind == "opt":
+        f = self.fc1(x.reshape(1, B, H), relu=True, pre_norm=ln2)
+        return self.fc2(f, residual=x.reshape(1, B, H), stats_out=s_out).reshape(B, 1, H)
+    return self.fc2(self.gate_up_proj(x, silu_mul=True, pre_norm=ln2), residual=x, stats_out=s_out)   # SwiGLU product in the GEMV epilogue
 
 
 DecoderLayer.forward_static = _layer_forward_static
@@ -216,6 +230,7 @@ class Decoder(nn.Module):
         super().__init__()
         self.cfg, self.rank, self.world, self.group, self.device = cfg, rank, world, group, torch.device(device)
         self.exchange = exchange
+        self._row_stats = None            # two quant.row_stats_buffer for the token step (made on first use)
         if source is None:
             source = SyntheticSource(cfg, seed, device)      # `source`: where the parameters come from (see SyntheticSource)
         H = cfg.hidden
@@ -283,10 +298,22 @@ class Decoder(nn.Module):
         else:
             rope = (self.rope_cos, self.rope_sin)
         from quant import add_norm
-        x, delta = x.contiguous(), None
+        x = x.contiguous()
+        # measured on one B200: a gain up to 8 sequences, a loss at 16 (every CTA of the consuming GEMV normalises all
+        # rows it stages, so the work grows with the batch while the launch it saves does not)
+        fold = self.cfg.fold_norms and x.shape[0] <= self.cfg.fold_norms_max_batch and self.cfg.hidden <= 8192
+        if fold and self._row_stats is None:
+            from quant import row_stats_buffer
+            self._row_stats = tuple(row_stats_buffer(self.cfg.hidden, x.device) for _ in range(2))
+        have = False                                     # the first layer's input comes from the embedding: no statistics
         for layer in self.layers:
-            x, delta = layer.forward_static(x, delta, pos_t, rope)
-        _, h = add_norm(x, delta, *_norm_args(self.final_norm))
+            if fold:
+                mid, out = self._row_stats
+                x = layer.forward_static(x, pos_t, rope, (out if have else None, mid, out))
+                have = True
+            else:
+                x = layer.forward_static(x, pos_t, rope)
+        _, h = add_norm(x, None, *_norm_args(self.final_norm))
         logits = h[:, -1] @ self.lm_head.t()
         if self.world > 1 and self.exchange is not None:
             # each rank's best (logit, vocabulary index) of its shard; ties go to the lowest rank = lowest index

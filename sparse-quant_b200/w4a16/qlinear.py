@@ -40,11 +40,14 @@ class WALinear(nn.Module):
             self.register_buffer("bias", None)
 
     @torch.no_grad()
-    def forward(self, x, relu: bool = False, residual=None, silu_mul: bool = False):
+    def forward(self, x, relu: bool = False, residual=None, silu_mul: bool = False, pre_norm=None, stats_out=None):
         """x fp16 [..., K] -> fp16 [..., N].  The reference requires 3-D input (gemm_quant.cu:73);
         2-D and >3-D inputs are viewed as [1, tokens, K] here.  Epilogues fused into the kernel: relu=True (the
         ReLU after OPT's fc1), residual (fp16 [..., N], added to the output), silu_mul=True (a fuse_gate_up linear
-        at up to 32 tokens: returns silu(gate) * up, [..., N / 2])."""
+        at up to 32 tokens: returns silu(gate) * up, [..., N / 2]), pre_norm = (weight, bias or None, eps, rms, stats):
+        x is the un-normalised input and the LayerNorm / RMSNorm in front of the linear runs inside the decode kernel,
+        from the row statistics `stats` that the linear producing x left with stats_out=stats (up to 16 tokens; as its
+        own launch otherwise, or when stats is None)."""
         shape = x.shape
         x3 = x if x.dim() == 3 else x.reshape(1, -1, shape[-1])
         if not x3.is_contiguous():
@@ -56,6 +59,10 @@ class WALinear(nn.Module):
             extra["silu_mul"] = True
         if residual is not None:
             extra["residual"] = residual if residual.is_contiguous() else residual.contiguous()
+        if pre_norm is not None:
+            extra["pre_norm"] = pre_norm
+        if stats_out is not None:
+            extra["stats_out"] = stats_out
         y = gemm_awq_bias(x3, self.weight, self.zeros_scales, self.bias, self.out_features, self.group_size,
                           static_weights=self.static_weights, **extra)
         n_out = self.out_features // 2 if silu_mul else self.out_features

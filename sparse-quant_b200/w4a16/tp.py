@@ -139,8 +139,13 @@ class ColumnParallelWALinear(nn.Module):
         w, zs, b = shard_column(full.weight, full.zeros_scales, full.bias, self.n0, self.n1)
         self.linear = _from_buffers(w, zs, b, g)
 
-    def forward(self, x, relu: bool = False):
-        return self.linear(x, relu=relu) if relu else self.linear(x)
+    def forward(self, x, relu: bool = False, pre_norm=None):
+        extra = {}
+        if relu:
+            extra["relu"] = True
+        if pre_norm is not None:
+            extra["pre_norm"] = pre_norm
+        return self.linear(x, **extra)
 
 
 class PeerExchange:
@@ -257,7 +262,9 @@ class RowParallelWALinear(nn.Module):
         self.rank = rank
         self.exchange = exchange
 
-    def forward(self, x_local):
+    def forward(self, x_local, residual=None, stats_out=None):
+        """`residual` (the same on all ranks) is added once to the summed output; stats_out: a quant.row_stats_buffer
+        that receives the row statistics of the output (up to 16 tokens, decode kernels only)."""
         tokens = x_local.numel() // x_local.shape[-1]
         if self.exchange is not None and tokens <= 32 and tokens * self.linear.out_features <= self.exchange.capacity:
             from quant import gemm_awq_allreduce
@@ -267,12 +274,16 @@ class RowParallelWALinear(nn.Module):
                 x3 = x3.contiguous()
             y = gemm_awq_allreduce(x3, lin.weight, lin.zeros_scales, self.full_bias, lin.out_features, lin.group_size,
                                    self.k_config, self.exchange.buffers, self.exchange.world, self.exchange.rank,
-                                   self.exchange.capacity, static_weights=lin.static_weights)
+                                   self.exchange.capacity, static_weights=lin.static_weights,
+                                   residual=None if residual is None else residual.reshape(1, tokens, lin.out_features).contiguous(),
+                                   stats_out=stats_out)
             return y.reshape(*x_local.shape[:-1], lin.out_features)
+        if self.world == 1 and residual is not None:
+            return self.linear(x_local, residual=residual, stats_out=stats_out)
         y = self.linear(x_local)
         if self.world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
-        return y
+        return y if residual is None else y + residual
 
 
 def mark_static(module: nn.Module, flag: bool = True):
