@@ -46,7 +46,7 @@ class DecoderConfig:
     # token step: normalisations folded into the GEMVs that consume them and residual adds into the GEMVs that produce
     # the block outputs (5 launches per layer); False keeps them as separate add+norm launches (7 per layer)
     fold_norms: bool = True
-    fold_norms_max_batch: int = 8
+    fold_norms_max_batch: int = 4
 
     @staticmethod
     def opt_6_7b():
@@ -299,8 +299,9 @@ class Decoder(nn.Module):
             rope = (self.rope_cos, self.rope_sin)
         from quant import add_norm
         x = x.contiguous()
-        # measured on one B200: a gain up to 8 sequences, a loss at 16 (every CTA of the consuming GEMV normalises all
-        # rows it stages, so the work grows with the batch while the launch it saves does not)
+        # measured: a gain up to 4 sequences (3 % on one B200, 8 % on four), none at 8, a loss at 16 - every CTA of the
+        # consuming GEMV normalises all rows it stages, so the work grows with the batch while the launch it saves does
+        # not, and from 5 sequences on the statistics take the small GEMVs off the two-CTAs-per-SM kernel
         fold = self.cfg.fold_norms and x.shape[0] <= self.cfg.fold_norms_max_batch and self.cfg.hidden <= 8192
         if fold and self._row_stats is None:
             from quant import row_stats_buffer
