@@ -47,3 +47,36 @@ def test_decoder_logits_match_dense_reference(kind, monkeypatch):
     static, _, _ = model.generate_graphed(ids, 6, use_graph=False)
     assert torch.equal(static, graphed)
     assert (eager == graphed).float().mean().item() >= 0.75      # argmax ties may flip between attention variants
+
+
+@pytest.mark.parametrize("kind", ["opt", "llama"])
+def test_token_step_with_folded_normalisations(kind):
+    """Five launches per layer (residual adds in the producing GEMVs, normalisations inside the consuming ones, row
+    statistics in between) against seven: the hidden state going into the final normalisation agrees, and the folded
+    step really launches fewer kernels."""
+    import quant
+    from w4a16.models import Decoder, DecoderConfig
+    if kind == "opt":
+        cfg = DecoderConfig("opt", layers=4, hidden=1024, heads=8, ffn=4096, vocab=512, group_size=128, max_positions=64)
+    else:
+        cfg = DecoderConfig("llama", layers=4, hidden=1024, heads=8, ffn=2752, vocab=512, group_size=64, max_positions=64)
+    B = 3
+    assert B <= cfg.fold_norms_max_batch
+    model = Decoder(cfg, device="cuda", seed=9).mark_static()
+    ids = torch.randint(0, cfg.vocab, (B, 12), device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    arange = torch.arange(32, device="cuda")
+    outs, launches = [], []
+    for fold in (False, True):
+        cfg.fold_norms = fold
+        for layer in model.layers:
+            layer.cfg.fold_norms = fold
+        model.reset(B, 32)
+        tok = model(ids).argmax(-1, keepdim=True)
+        pos_t = torch.full((1,), 12, dtype=torch.long, device="cuda")
+        n0 = quant.launch_count()
+        nxt = model.step_static(tok, pos_t, arange)
+        torch.cuda.synchronize()
+        launches.append(quant.launch_count() - n0)
+        outs.append(nxt)
+    assert launches[1] <= launches[0] - 2 * (cfg.layers - 1) - 1     # two launches fewer per layer, one fewer in the first
+    assert (outs[0] == outs[1]).float().mean().item() >= 0.66        # greedy tokens of random-weight models: near ties may flip
