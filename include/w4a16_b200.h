@@ -211,6 +211,10 @@ int w4a16_exchange_status(const void* buffer, unsigned* epoch, int* error);
  * rank's best logit of its vocabulary shard. */
 int w4a16_exchange_allgather(const void* in, void* out, int words, void* const* buffers, int world, int rank,
                              size_t capacity_elems, void* stream);
+/* 1 if w4a16_gemm_allreduce(_residual) takes this problem on the current device (at most 32 tokens in one pass whose
+ * grid fits the GPU in one wave), else 0: decide between the fused exchange and a library all-reduce from the shapes,
+ * identically on every rank. */
+int w4a16_allreduce_supported(int tokens, int N, int K, int k_config, int group_size, int world);
 int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
                          void* out, int tokens, int N, int K, int group_size, int k_config,
                          void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,

@@ -25,6 +25,19 @@ bool aux_programmatic_launch() { return g_aux_programmatic.load(std::memory_orde
 
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+int device_sm_count()
+{
+    static int cache[64] = {};         // benign race: the query is idempotent
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
+    if (!cache[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) { (void)cudaGetLastError(); v = 148; }
+        cache[dev] = v;
+    }
+    return cache[dev];
+}
+
 // Allocated once per device (first use; outside stream capture), never freed.  Word 0 is the error word (only ever
 // raised by kernels, cleared by w4a16_device_error_clear); word 1 is a generation counter the decode kernel bumps.
 int* device_error_word()

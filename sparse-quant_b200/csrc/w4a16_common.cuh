@@ -166,6 +166,7 @@ struct GemmArgs {
     bool silu_mul = false; // W4A16_FLAG_SILU_MUL: gate / up tiles alternate, out = silu(gate) * up, [tokens, N / 2] (decode kernels)
     const __half* residual = nullptr;   // [tokens, N] added after bias / ReLU, or null
     const ExchangeArgs* exchange = nullptr;   // non-null: out = sum over ranks of this rank's partial product (decode kernel only)
+    bool plan_only = false;                   // check the arguments and the launch plan, launch nothing
     // non-null: x is normalised row by row (LayerNorm, or RMSNorm when norm_rms) after it is staged - the launch of
     // the normalisation kernel in front of the GEMV is saved (<= 16 tokens, one-CTA-per-SM decode kernel only).  The
     // row statistics come from the GEMV that produced x (row_stats_in = its row_stats_out).
@@ -180,6 +181,7 @@ struct GemmArgs {
 // Launch, optionally with programmatic stream serialization (the grid may then be scheduled while the previous
 // kernel of the stream drains).  Only for kernels that execute griddepcontrol.wait before they touch anything the
 // stream's earlier work produces.
+int device_sm_count();                           // SMs of the current device (cached); 148 when the query fails
 bool aux_programmatic_launch();                  // tuning switch (w4a16_tune_aux_launch), default off
 template <typename... KArgs, typename... Args>
 cudaError_t launch_after_previous(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)

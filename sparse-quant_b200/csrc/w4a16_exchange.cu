@@ -207,6 +207,27 @@ extern "C" int w4a16_gemm_allreduce_residual(const void* x, const void* qweight,
     return launch_skinny(a, (cudaStream_t)stream);
 }
 
+// Whether w4a16_gemm_allreduce(_residual) accepts this problem: the fused exchange needs one pass of at most 32 tokens
+// whose whole grid is resident at once (the ranks wait for each other inside the kernel).  Deterministic from the
+// shapes (and the SM count of the current device), so all ranks of a homogeneous node agree and can choose the
+// library all-reduce up front instead.
+extern "C" int w4a16_allreduce_supported(int tokens, int N, int K, int k_config, int group_size, int world)
+{
+    if (group_size != 32 && group_size != 64 && group_size != 128) return 0;
+    if (tokens <= 0 || tokens > 32 || N <= 0 || K <= 0 || (N % 32) || (K % group_size) || k_config < K) return 0;
+    if (world < 1 || world > kExchangeMaxWorld) return 0;
+    static unsigned char dummy;
+    ExchangeArgs ex;
+    for (int d = 0; d < kExchangeMaxWorld; ++d) ex.peer[d] = d < world ? &dummy : nullptr;
+    ex.world = world; ex.rank = 0; ex.capacity = (long long)tokens * N; ex.k_config = k_config;
+    GemmArgs a;
+    a.x = nullptr; a.qw = nullptr; a.zs = nullptr; a.bias = nullptr; a.out = nullptr;
+    a.tokens = tokens; a.N = N; a.K = K; a.g = group_size; a.static_weights = false;
+    a.exchange = &ex;
+    a.plan_only = true;
+    return launch_skinny(a, nullptr) == W4A16_OK ? 1 : 0;
+}
+
 extern "C" int w4a16_gemm_allreduce(const void* x, const void* qweight, const void* zeros_scales, const void* bias,
                                     void* out, int tokens, int N, int K, int group_size, int k_config,
                                     void* const* buffers, int world, int rank, size_t capacity_elems, void* stream,

@@ -534,18 +534,7 @@ struct Config { int tn, splits, depth, ahead, rp, swizzled, x_offset, w_offset, 
 int g_force_tn = 0, g_force_splits = 0, g_force_depth = 0, g_force_ahead = -1;
 unsigned long long* g_timeline = nullptr;
 
-int sm_count()
-{
-    static int cache[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (!cache[dev]) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) { (void)cudaGetLastError(); v = 148; }
-        cache[dev] = v;
-    }
-    return cache[dev];
-}
+int sm_count() { return device_sm_count(); }
 
 int slot_bytes(int g) { return kUnitTiles * 512 + (kUnitK / g) * 128; }
 
@@ -706,8 +695,8 @@ int launch_gemv(const GemmArgs& a, cudaStream_t st)
 
     GemvParams p;
     p.zs = a.zs; p.bias = a.bias; p.out = a.out;
-    p.error = device_error_word();
-    if (!p.error) return W4A16_ERR_CUDA;
+    p.error = a.plan_only ? nullptr : device_error_word();
+    if (!p.error && !a.plan_only) return W4A16_ERR_CUDA;
     p.world = 0; p.rank = 0; p.capacity = 0; p.self = nullptr; p.wait_budget_ns = exchange_wait_budget_ns();
     for (int d = 0; d < kExchangeMaxWorld; ++d) p.peer[d] = nullptr;
     if (a.exchange) {
@@ -745,6 +734,7 @@ int launch_gemv(const GemmArgs& a, cudaStream_t st)
     dim3 grid(grid_x, c.splits, passes);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
     if (a.exchange && grid.z != 1) return W4A16_ERR_TOO_LARGE;
+    if (a.plan_only) return (a.g == 128 || a.g == 64 || a.g == 32) ? W4A16_OK : W4A16_ERR_GROUP_SIZE;
     CUtensorMap wmap, xmap;
     {
         // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words

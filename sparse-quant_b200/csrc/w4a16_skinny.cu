@@ -750,7 +750,7 @@ int max_clusters_instance(int sp)
 {
     static int cache[64][9] = {};      // benign race: the query is idempotent
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148 / sp;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return device_sm_count() / sp;
     if (cache[dev][sp]) return cache[dev][sp];
     int n = 0;
     const int smem = 200 * 1024;
@@ -770,15 +770,15 @@ int max_clusters_instance(int sp)
     } else {
         (void)cudaGetLastError();
     }
-    if (n <= 0) n = 148 / sp;          // query unavailable: assume perfect packing
+    if (n <= 0) n = device_sm_count() / sp;          // query unavailable: assume perfect packing
     cache[dev][sp] = n;
     return n;
 }
 
 int max_clusters(int tg, int g, int sp)
 {
-    if (sp <= 1) return 148;
-    if (tg != 4) return 148 / sp;
+    if (sp <= 1) return device_sm_count();
+    if (tg != 4) return device_sm_count() / sp;
     switch (g) {
         case 128: return max_clusters_instance<4, 128>(sp);
         case 64:  return max_clusters_instance<4, 64>(sp);
@@ -806,7 +806,8 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4, int min_wn =
     if (g_force_depth && g_force_depth < c.depth) c.depth = g_force_depth;
     // out-feature tiles per CTA: about one CTA per SM in a single wave
     c.wn = min_wn;
-    while (c.wn < kWarps && (long long)((n_tiles + c.wn - 1) / c.wn) * c.splits > 148) c.wn <<= 1;
+    const int sms = device_sm_count();
+    while (c.wn < kWarps && (long long)((n_tiles + c.wn - 1) / c.wn) * c.splits > sms) c.wn <<= 1;
     // every K slice of a CTA should own at least one 128-k unit
     while (c.wn < kWarps && (kWarps / c.wn) * c.splits > units) c.wn <<= 1;
     if (g_force_wn) c.wn = g_force_wn;
@@ -819,7 +820,7 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4, int min_wn =
             for (int sp = 1; sp <= 8; ++sp) {
                 if (sp > units) break;
                 const long long ctas = (long long)((n_tiles + wn - 1) / wn) * sp;
-                if (ctas > 148 || ctas / sp > max_clusters(c.tg, g, sp)) continue;      // one wave, as the device packs clusters
+                if (ctas > sms || ctas / sp > max_clusters(c.tg, g, sp)) continue;      // one wave, as the device packs clusters
                 const int room = kSmemBudget - stage_bytes(rows, K, sp, kUnitK, c.tg, g);
                 int depth = room / ring1;
                 if (depth < 2) continue;
@@ -829,7 +830,7 @@ Config pick_config(int tokens, int N, int K, int g, int max_tg = 4, int min_wn =
                 if (score > best) { best = score; c.wn = wn; c.splits = sp; c.depth = depth; }
             }
         }
-        if (best < 0) c.splits = 8;      // nothing fits: the caller falls back to two passes of 16 tokens
+        if (best < 0) { c.splits = 8; c.depth = 0; }      // nothing fits in one wave: two passes of 16 tokens (no exchange) or refused
     }
     return c;
 }
@@ -940,8 +941,8 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
 
     SkinnyParams p;
     p.x = a.x; p.qw = reinterpret_cast<const uint4*>(a.qw); p.zs = a.zs; p.bias = a.bias; p.out = a.out;
-    p.error = device_error_word();
-    if (!p.error) return W4A16_ERR_CUDA;
+    p.error = a.plan_only ? nullptr : device_error_word();
+    if (!p.error && !a.plan_only) return W4A16_ERR_CUDA;
     p.world = 0; p.rank = 0; p.capacity = 0; p.self = nullptr; p.wait_budget_ns = exchange_wait_budget_ns();
     for (int d = 0; d < kExchangeMaxWorld; ++d) p.peer[d] = nullptr;
     if (a.exchange) {
@@ -972,7 +973,10 @@ int launch_skinny(const GemmArgs& a, cudaStream_t st)
     dim3 grid((n_tiles + c.wn - 1) / c.wn, c.splits, (a.tokens + tok - 1) / tok);
     if (grid.z > 65535) return W4A16_ERR_BAD_SHAPE;
     if (a.exchange && grid.z != 1) return W4A16_ERR_TOO_LARGE;
+    // the ranks spin on each other inside the kernel: every CTA of the grid must be resident at once
+    if (a.exchange && (long long)grid.x * grid.y > device_sm_count()) return W4A16_ERR_TOO_LARGE;
     if ((a.norm_weight || a.row_stats_out) && grid.z != 1) return W4A16_ERR_BAD_ALGO;
+    if (a.plan_only) return (a.g == 128 || a.g == 64 || a.g == 32) ? W4A16_OK : W4A16_ERR_GROUP_SIZE;
     // the packed matrix as a 2-D tensor of 32-bit words: [K/32 rows][N/32 * 128 words], box = 4 rows x 128 words
     CUtensorMap wmap;
     {

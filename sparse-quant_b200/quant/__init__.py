@@ -53,6 +53,7 @@ C_ABI = {
     "w4a16_exchange_allgather": (_ci, [_vp, _vp, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz, _vp]),
     "w4a16_gemm_allreduce": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci, _ci, _sz,
                                    _vp, ctypes.c_uint]),
+    "w4a16_allreduce_supported": (_ci, [_ci, _ci, _ci, _ci, _ci, _ci]),
     "w4a16_gemm_allreduce_residual": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.POINTER(_vp), _ci,
                                             _ci, _sz, _vp, ctypes.c_uint]),
     "w4a16_decode_attention": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, ctypes.c_float, _vp]),

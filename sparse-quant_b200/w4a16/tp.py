@@ -261,12 +261,26 @@ class RowParallelWALinear(nn.Module):
         self.world = world
         self.rank = rank
         self.exchange = exchange
+        self._fused_cache = {}
+
+    def _fused_ok(self, tokens: int) -> bool:
+        """Whether the fused exchange takes this many tokens for this shard (asked once per token count; the answer
+        depends only on shapes, so every rank decides alike)."""
+        ok = self._fused_cache.get(tokens)
+        if ok is None:
+            import quant
+            lin = self.linear
+            ok = bool(quant.load_library().w4a16_allreduce_supported(tokens, lin.out_features, lin.in_features, self.k_config,
+                                                                     lin.group_size, self.exchange.world))
+            self._fused_cache[tokens] = ok
+        return ok
 
     def forward(self, x_local, residual=None, stats_out=None):
         """`residual` (the same on all ranks) is added once to the summed output; stats_out: a quant.row_stats_buffer
         that receives the row statistics of the output (up to 16 tokens, decode kernels only)."""
         tokens = x_local.numel() // x_local.shape[-1]
-        if self.exchange is not None and tokens <= 32 and tokens * self.linear.out_features <= self.exchange.capacity:
+        if self.exchange is not None and tokens <= 32 and tokens * self.linear.out_features <= self.exchange.capacity \
+                and self._fused_ok(tokens):
             from quant import gemm_awq_allreduce
             lin = self.linear
             x3 = x_local.reshape(1, tokens, x_local.shape[-1])

@@ -94,3 +94,15 @@ def test_exchange_argument_errors(exchange):
     assert lib.w4a16_exchange_bytes(9, 10) == 0
     buf = ctypes.c_void_p()
     assert lib.w4a16_exchange_alloc(2, 0, ctypes.byref(buf)) == 2
+
+
+def test_allreduce_supported_predicate():
+    """The host-side predicate agrees with what the fused call accepts: decode-sized shards yes, more than 32 tokens
+    or a shard whose grid cannot be resident in one wave no."""
+    import quant
+    lib = quant.load_library()
+    assert lib.w4a16_allreduce_supported(8, 4096, 2048, 2048, 128, 8) == 1
+    assert lib.w4a16_allreduce_supported(32, 4096, 1376, 1408, 64, 8) == 1
+    assert lib.w4a16_allreduce_supported(33, 4096, 2048, 2048, 128, 8) == 0
+    assert lib.w4a16_allreduce_supported(8, 4096, 2048, 1024, 128, 8) == 0      # k_config below K
+    assert lib.w4a16_allreduce_supported(8, 4096, 2048, 2048, 128, 9) == 0      # more ranks than the buffers hold
