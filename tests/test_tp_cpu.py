@@ -180,3 +180,15 @@ def test_gate_up_fusion_alternates_tiles_of_32_out_features():
     a, c = split_gate_up(y)
     assert torch.equal(a, y.reshape(2, n // 32, 2, 32)[:, :, 0].reshape(2, n))
     assert torch.equal(c, y.reshape(2, n // 32, 2, 32)[:, :, 1].reshape(2, n))
+
+
+def test_allreduce_supported_is_host_logic():
+    """The predicate the row-parallel layer asks before it takes the fused exchange is pure host arithmetic: it answers
+    without a GPU, identically for identical shapes."""
+    import quant
+    lib = quant.load_library()
+    assert lib.w4a16_allreduce_supported(8, 4096, 2048, 2048, 128, 8) == 1
+    assert lib.w4a16_allreduce_supported(32, 4096, 1344, 1408, 64, 8) == 1
+    assert lib.w4a16_allreduce_supported(33, 4096, 2048, 2048, 128, 8) == 0      # more than one pass
+    assert lib.w4a16_allreduce_supported(8, 4096, 2048, 1024, 128, 8) == 0       # k_config below this rank's K
+    assert lib.w4a16_allreduce_supported(8, 4100, 2048, 2048, 128, 8) == 0       # N not a multiple of 32
