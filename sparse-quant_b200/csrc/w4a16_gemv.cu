@@ -284,15 +284,9 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
 
         int slot = 0;
         uint32_t phase = 0;
-        bool landed = false;                                // the coming unit was seen complete by the probe below
         for (int i = 0; i < n_units; ++i) {
-            if (!landed) {
-                const bool ok = mbar_wait(bars + slot * 8, phase, abort_flag, kWaitBudgetNs);
-                if (!__all_sync(0xffffffffu, ok)) break;
-            }
-            // probe the next unit's barrier while this one is computed (see the 16-warp kernel)
-            const int nslot = slot + 1 == depth ? 0 : slot + 1;
-            const bool next_landed = i + 1 < n_units && mbar_test_wait(bars + nslot * 8, nslot == 0 ? phase ^ 1u : phase);
+            const bool ok = mbar_wait(bars + slot * 8, phase, abort_flag, kWaitBudgetNs);
+            if (!__all_sync(0xffffffffu, ok)) break;
             if (tl && i == 0) tl[2] = globaltimer_ns();
 
             const int u = wu0 + i;
@@ -350,7 +344,6 @@ gemv_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
                 if (i + depth < n_units) { issue_w(i + depth, slot); issue_x(i + depth, slot); }
                 if (i + depth + p.ahead < n_units) prefetch_w(i + depth + p.ahead);
             }
-            landed = __all_sync(0xffffffffu, next_landed);
             if (++slot == depth) { slot = 0; phase ^= 1u; }
         }
     }

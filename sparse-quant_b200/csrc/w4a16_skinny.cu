@@ -479,16 +479,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
         }
         int slot = 0;
         uint32_t phase = 0;
-        bool landed = false;                                // the coming unit was seen complete by the probe below
         for (int i = 0; i < n_units; ++i) {
-            if (!landed) {
-                const bool ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * slot, phase, abort_flag, kWaitBudgetNs));
-                if (!ok) break;
-            }
-            // probe the NEXT unit's barrier now: the answer arrives while this unit is computed, and a unit that has
-            // landed by then (the usual case once the ring is full) costs no barrier round trip in the next iteration
-            const int nslot = slot + 1 == depth ? 0 : slot + 1;
-            const bool next_landed = i + 1 < n_units && mbar_test_wait(bars + 8 * nslot, nslot == 0 ? phase ^ 1u : phase);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * slot, phase, abort_flag, kWaitBudgetNs));
+            if (!ok) break;
             if (tl && i == 0) tl[3] = globaltimer_ns();
             const int u = wu0 + i;
             if (!kDebug || (p.debug_mode & 1) == 0)
@@ -500,7 +493,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) skinny_kernel(const __grid_con
             if (i + depth < n_units && sm100::elect_one())
                 issue_unit<G, kUnitK>(ring_addr + slot * (uint32_t)sizeof(SlotT), bars + 8 * slot, &wmap, zs_next + (size_t)(i + depth) * zs_step, p.N,
                               u + depth, nt, groups);
-            landed = __all_sync(0xffffffffu, next_landed);
             if (++slot == depth) { slot = 0; phase ^= 1u; }
         }
     }
