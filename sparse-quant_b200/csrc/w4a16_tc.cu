@@ -10,19 +10,25 @@
 //
 // One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6-9 dequantisers, 4 and 10 TMA, 5 MMA).
 //
-// What sets the pace is the ISSUE cost of the tensor-core instructions in the one thread that may issue them
-// (measured on B200 with a loop of nothing but MMAs, 148 CTAs): a tcgen05.mma takes about 94 cycles to issue whatever
-// its N (it executes in N/2 cycles, so only N = 256 hides the issue), and a tcgen05.commit costs about 205 cycles.
-// A pipeline step is therefore 128 k = eight MMAs behind ONE commit (8 x 94 + 205 = 957 issue cycles against 1024
-// cycles of tensor time at 256 tokens); with 64-k steps and one or two commits per step the same kernel ran at
-// 750 to 790 cycles per 512 cycles of tensor time, whatever the token tile, and no change to the other roles moved it.
+// What set the pace of earlier versions was the ISSUE cost of the tensor-core instructions in the one thread that may
+// issue them (measured on B200 with a loop of nothing but MMAs, 148 CTAs): from a loop that a single lane enters a
+// tcgen05.mma issues every 94 cycles whatever its N (it executes in N/2 cycles) and a tcgen05.commit adds about 205;
+// from a loop walked by the whole warp with an elected issuer (see elect_one) 45 / 73.5 / 137.5 cycles per MMA at
+// N = 64 / 128 / 256 with the commit hidden at N = 256.  Hence: stages of 128 k (eight MMAs per pair of commits), the
+// warp-wide loop, and barrier probes issued ahead of the MMAs in front of them.  With 64-k stages, a single issuing
+// lane and one or two commits per stage the same kernel ran at 750 to 790 cycles per 512 cycles of tensor time,
+// whatever the token tile, and no change to the other roles moved it.
 //
 // Rings (a stage = 128 k):
-//   x ring   (shared memory, 128-byte swizzle, K-major): the activation tile as two 64-k sub-tiles, filled by warp 4
-//            with two tensor copies on one mbarrier, read only by the MMA.
+//   x ring   (shared memory, 128-byte swizzle, K-major): the activation tile as two 64-k sub-tiles, each with its own
+//            mbarrier, filled by warp 4 with one tensor copy each, read only by the MMA.  The first sub-tile is
+//            released by a commit of its own after the stage's first four MMAs, so that its refill starts half a
+//            stage earlier (with whole-stage release the MMA warp waited for activations 10 % of its time at 256
+//            tokens; with this 1 %).
 //   A ring   (tensor memory, 64 columns per slot, same depth and index as the x ring): the dequantised fp16 weights
-//            of the stage, written by the dequantisers, read by the MMA.  One tcgen05.commit per stage releases the
-//            x stage and the A slot together (barrier `consumed`, waited on by warp 4 and by the dequantisers).
+//            of the stage, written by the dequantisers, read by the MMA.  The commit at the end of a stage releases
+//            the second x sub-tile and the A slot together (barrier `consumed`, waited on by warp 4 and by the
+//            dequantisers).
 //   W ring   (shared memory, own depth): the stage's packed weight tiles (a k-tile row of the format is contiguous:
 //            plain bulk copies) and the (zero, scale) row(s), filled by warp 10, read only by the dequantisers and
 //            released as soon as they hold the words in registers.
@@ -32,8 +38,8 @@
 //            with tcgen05.st.16x128b - the packed layout is already that fragment order - so the dequantised weights
 //            never touch shared memory.
 //   warp 5   MMA issuer: tcgen05.mma kind::f16 with A from tensor memory and B from the swizzled shared-memory
-//            tile, eight K=16 instructions per stage; the coming stage's barriers are probed before the MMAs are
-//            issued, so that in steady state no barrier round trip sits between two stages.
+//            tile, eight K=16 instructions and two commits per stage; the barriers needed next are probed before
+//            the MMAs in front of them are issued, so that in steady state no barrier round trip sits between them.
 //   warps0-3,6-9 epilogue (after their last dequant step of the tile): tcgen05.ld the accumulator,
 //            fp32 -> fp16, bias add, transposed store to out[token, out-feature].
 // No cluster fan-out is used anywhere.  Every mbarrier wait is bounded; on a timeout the CTA raises an error word
@@ -73,7 +79,7 @@ struct TcCfg {
     static constexpr int kWRingOff = kStages * kXBytes;
     static constexpr int kBarOff   = kWRingOff + kWStages * kWStageBytes;
     static constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kBarOff + kBarrierBytes;
-    static constexpr int kBarriers = 3 * kStages + 2 * kWStages + 3;
+    static constexpr int kBarriers = 5 * kStages + 2 * kWStages + 3;
     static_assert(8 * kBarriers + 12 <= kBarrierBytes, "barrier area");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
     static_assert(kACol + 64 * kStages <= kTmemCols, "TMEM budget");
@@ -105,13 +111,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + Cfg::kBarOff;
-    // barrier layout (8 B each): xfull[S], afull[S], consumed[S], wfull[SW], wempty[SW], dfull, dempty, epi ; then
-    // tmem ptr, abort flag, last flag
-    auto xfull_bar    = [&](int s) { return bar_base + 8u * s; };
-    auto afull_bar    = [&](int s) { return bar_base + 8u * (S + s); };
-    auto consumed_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-    auto wfull_bar    = [&](int s) { return bar_base + 8u * (3 * S + s); };
-    auto wempty_bar   = [&](int s) { return bar_base + 8u * (3 * S + SW + s); };
+    // barrier layout (8 B each): xfull[2S] (one per 64-k half), afull[S], consumed[S], xhalf[S], wfull[SW], wempty[SW],
+    // dfull, dempty, epi ; then tmem ptr, abort flag, last flag
+    auto xfull_bar    = [&](int h) { return bar_base + 8u * h; };                     // h = 2 * stage + half
+    auto afull_bar    = [&](int s) { return bar_base + 8u * (2 * S + s); };
+    auto consumed_bar = [&](int s) { return bar_base + 8u * (3 * S + s); };           // A slot and second x half free
+    auto xhalf_bar    = [&](int s) { return bar_base + 8u * (4 * S + s); };           // first x half free
+    auto wfull_bar    = [&](int s) { return bar_base + 8u * (5 * S + s); };
+    auto wempty_bar   = [&](int s) { return bar_base + 8u * (5 * S + SW + s); };
     const uint32_t dfull_bar = bar_base + 8u * (Cfg::kBarriers - 3), dempty_bar = dfull_bar + 8u, epi_bar = dfull_bar + 16u;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kBarOff + 8 * Cfg::kBarriers);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -120,7 +127,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(xfull_bar(s), 1); mbar_init(afull_bar(s), 8); mbar_init(consumed_bar(s), 1); }
+        for (int s = 0; s < S; ++s) {
+            mbar_init(xfull_bar(2 * s), 1); mbar_init(xfull_bar(2 * s + 1), 1);
+            mbar_init(afull_bar(s), 8); mbar_init(consumed_bar(s), 1); mbar_init(xhalf_bar(s), 1);
+        }
         for (int s = 0; s < SW; ++s) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 8); }
         mbar_init(dfull_bar, 1);
         mbar_init(dempty_bar, 8);
@@ -164,13 +174,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 k_range(item, ks0, ks1);
                 int kcoord = ks0 * kBlockK;
                 for (int ks = ks0; ks < ks1; ++ks) {
+                    // the two 64-k halves of a stage are released one after the other (the first one by a commit in
+                    // the middle of the stage's MMAs): each refill starts half a stage earlier than a whole-stage
+                    // release would allow
+                    const uint32_t dst = smem_base + st * Cfg::kXBytes;
+                    ok = mbar_wait(xhalf_bar(st), phase ^ 1u, abort_flag, kWaitBudgetNs);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(xfull_bar(2 * st), Cfg::kXSubBytes);
+                    tma_load_2d(dst, &x_map, kcoord, tb * TOK, xfull_bar(2 * st));
                     ok = mbar_wait(consumed_bar(st), phase ^ 1u, abort_flag, kWaitBudgetNs);
                     if (!ok) break;
-                    const uint32_t bar = xfull_bar(st);
-                    const uint32_t dst = smem_base + st * Cfg::kXBytes;
-                    mbar_arrive_expect_tx(bar, Cfg::kXBytes);
-                    tma_load_2d(dst, &x_map, kcoord, tb * TOK, bar);
-                    tma_load_2d(dst + Cfg::kXSubBytes, &x_map, kcoord + kSubK, tb * TOK, bar);
+                    mbar_arrive_expect_tx(xfull_bar(2 * st + 1), Cfg::kXSubBytes);
+                    tma_load_2d(dst + Cfg::kXSubBytes, &x_map, kcoord + kSubK, tb * TOK, xfull_bar(2 * st + 1));
                     kcoord += kBlockK;
                     if (++st == S) { st = 0; phase ^= 1u; }
                 }
@@ -260,11 +275,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                     const long long c0 = clock64();
                     ok = __all_sync(0xffffffffu, mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs));
                     const long long c1 = clock64();
-                    ok = ok && __all_sync(0xffffffffu, mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs));
+                    ok = ok && __all_sync(0xffffffffu, mbar_wait(xfull_bar(2 * st), phase, abort_flag, kWaitBudgetNs));
                     acct[1] += c1 - c0; acct[2] += clock64() - c1;
 #else
                     ok = __all_sync(0xffffffffu, mbar_wait(afull_bar(st), phase, abort_flag, kWaitBudgetNs) &&
-                                                 mbar_wait(xfull_bar(st), phase, abort_flag, kWaitBudgetNs));
+                                                 mbar_wait(xfull_bar(2 * st), phase, abort_flag, kWaitBudgetNs));
 #endif
                     if (!ok) break;
                 }
@@ -272,14 +287,33 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)(st * Cfg::kXBytes) >> 4);
                 const uint32_t a_tmem = tmem_base + Cfg::kACol + 64 * st;
                 const int cur = st;
-                if (++st == S) { st = 0; phase ^= 1u; }
-                const bool next_a = mbar_test_wait(afull_bar(st), phase);
-                const bool next_x = mbar_test_wait(xfull_bar(st), phase);
+                const uint32_t cur_phase = phase;
+                // first 64-k half: its activation sub-tile is released by a commit of its own
+                const bool second_x = mbar_test_wait(xfull_bar(2 * cur + 1), cur_phase);
                 if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < kBlockK / 16; ++kk)
-                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (Cfg::kXSubBytes >> 4) + 2 * (kk & 3)),
-                                   idesc, ((ks - ks0) | kk) != 0);
+                    for (int kk = 0; kk < 4; ++kk)
+                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + (uint64_t)(2 * kk), idesc, ((ks - ks0) | kk) != 0);
+                    tc_commit(xhalf_bar(cur));
+                }
+                __syncwarp();
+                if (!__all_sync(0xffffffffu, second_x)) {
+#ifdef W4A16_SKINNY_DEBUG
+                    const long long c1 = clock64();
+#endif
+                    ok = __all_sync(0xffffffffu, mbar_wait(xfull_bar(2 * cur + 1), cur_phase, abort_flag, kWaitBudgetNs));
+                    TC_ACCT(2, clock64() - c1);
+                    TC_ACCT(5, 1);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                if (++st == S) { st = 0; phase ^= 1u; }
+                const bool next_a = mbar_test_wait(afull_bar(st), phase);
+                const bool next_x = mbar_test_wait(xfull_bar(2 * st), phase);
+                if (elect_one()) {
+#pragma unroll
+                    for (int kk = 4; kk < 8; ++kk)
+                        mma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + (uint64_t)((Cfg::kXSubBytes >> 4) + 2 * (kk & 3)), idesc, 1);
                     tc_commit(consumed_bar(cur));
                 }
                 __syncwarp();
