@@ -831,8 +831,10 @@ def e2e_host(lib, weights, dev, stream, world, local_shape, calls):
 
 
 def prefill_sweep(lib, weights, dev, stream, peaks):
-    """tcgen05 GEMM: TFLOP/s = 2*M*N*K / time for M in {512, 2048, 8192} on the three shapes; median and minimum over
-    20 calls, each between its own CUDA events, rotating over the weight sets."""
+    """tcgen05 GEMM: TFLOP/s = 2*M*N*K / time for M in {512, 2048, 8192} on the three shapes.  Calls of less than
+    about 100 us are timed as 16 back-to-back launches in a CUDA graph rotating over the weight sets (median and
+    minimum of 7 replays): one eager call at a time leaves the GPU waiting for the host between launches (24 us in a
+    graph against 29 us eagerly at M = 512 on 4096 x 4096).  Longer calls: 20 eager calls, each between its own events."""
     rows = []
     sp = stream.cuda_stream
     for (K, N) in DECODE_SHAPES:
@@ -843,16 +845,18 @@ def prefill_sweep(lib, weights, dev, stream, peaks):
             ws_bytes = lib.w4a16_workspace_bytes(M, N, K, G)          # > 0 when the library wants to split K
             ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
 
-            def fn(i, M=M, K=K, N=N, x=x, o=o, ws=ws, ws_bytes=ws_bytes, sets=sets):
+            def fn(i, st=None, M=M, K=K, N=N, x=x, o=o, ws=ws, ws_bytes=ws_bytes, sets=sets):
                 qw, zs = sets[i % len(sets)]
                 r = lib.w4a16_gemm(x.data_ptr(), qw.data_ptr(), zs.data_ptr(), None, o.data_ptr(), M, N, K, G,
-                                   ws.data_ptr() if ws_bytes else None, ws_bytes, sp)
+                                   ws.data_ptr() if ws_bytes else None, ws_bytes, sp if st is None else st)
                 if r != 0:
                     raise RuntimeError(lib.w4a16_status_str(r).decode())
-            med, mn = time_calls(fn, stream, 20, warm=3)
+            in_graph = 2.0 * M * N * K < 1.2e11                       # below ~100 us at the rates measured here
+            med, mn = time_graph(fn, stream, 16) if in_graph else time_calls(fn, stream, 20, warm=3)
             tf = 2.0 * M * N * K / (med * 1e-3) / 1e12
             rows.append({"K": K, "N": N, "M": M, "ms": med, "ms_min": mn, "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
-                         "frac_of_nominal_2250": tf / 2250.0, "workspace_bytes": ws_bytes})
+                         "frac_of_nominal_2250": tf / 2250.0, "workspace_bytes": ws_bytes,
+                         "timed": "16 launches in a CUDA graph" if in_graph else "eager calls between events"})
             del x, o, ws
     flag = ctypes.c_int(0)
     lib.w4a16_device_error_flag(ctypes.byref(flag))
