@@ -8,7 +8,8 @@
 // out-features per CTA tile), the activations are "B" (N = 64/128/256 tokens), the fp32
 // accumulator D[out-feature lane][token column] lives in tensor memory.
 //
-// One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6-9 dequantisers, 4 and 10 TMA, 5 MMA).
+// One persistent CTA per SM, warp specialised (warp numbers: 0-3 and 6.. dequantisers, 4 and the last one TMA, 5 MMA;
+// 352 threads with the 256-token tile, 608 with the smaller ones, which have two more dequantiser groups).
 //
 // What set the pace of earlier versions was the ISSUE cost of the tensor-core instructions in the one thread that may
 // issue them (measured on B200 with a loop of nothing but MMAs, 148 CTAs): from a loop that a single lane enters a
@@ -30,17 +31,19 @@
 //            the second x sub-tile and the A slot together (barrier `consumed`, waited on by warp 4 and by the
 //            dequantisers).
 //   W ring   (shared memory, own depth): the stage's packed weight tiles (a k-tile row of the format is contiguous:
-//            plain bulk copies) and the (zero, scale) row(s), filled by warp 10, read only by the dequantisers and
+//            plain bulk copies) and the (zero, scale) row(s), filled by the last warp, read only by the dequantisers and
 //            released as soon as they hold the words in registers.
-//   warps0-3,6-9 dequantisers (two groups of four; group g takes the g-th 64-k half of every stage): read 16 B per
-//            lane per 32x32 tile from shared memory, expand the nibbles in registers, (t - z) * s with
+//   warps0-3,6.. dequantisers (groups of four; a pair of groups takes the two 64-k halves of a stage; with the 64- and
+//            128-token tiles, whose stages are shorter than a pair's latency chain, two pairs take stages in turn -
+//            measured 3-7 % there): read 16 B per lane per 32x32 tile from shared memory, expand the nibbles in
+//            registers, (t - z) * s with
 //            sub.ftz/mul.ftz (bit-exact with the reference), and write the fp16 result straight into tensor memory
 //            with tcgen05.st.16x128b - the packed layout is already that fragment order - so the dequantised weights
 //            never touch shared memory.
 //   warp 5   MMA issuer: tcgen05.mma kind::f16 with A from tensor memory and B from the swizzled shared-memory
 //            tile, eight K=16 instructions and two commits per stage; the barriers needed next are probed before
 //            the MMAs in front of them are issued, so that in steady state no barrier round trip sits between them.
-//   warps0-3,6-9 epilogue (after their last dequant step of the tile): tcgen05.ld the accumulator,
+//   warps0-3,6-9 epilogue (the first pair of groups, after their last dequant step of the tile): tcgen05.ld the accumulator,
 //            fp32 -> fp16, bias add, transposed store to out[token, out-feature].
 // No cluster fan-out is used anywhere.  Every mbarrier wait is bounded; on a timeout the CTA raises an error word
 // in global memory, drains and frees its tensor memory, and returns.
@@ -60,9 +63,15 @@ namespace {
 constexpr int kBlockN   = 128;                 // out-features per CTA tile (4 packed tiles)
 constexpr int kBlockK   = 128;                 // k per pipeline stage (4 packed tiles, eight MMAs, one commit)
 constexpr int kSubK     = 64;                  // k per swizzled activation sub-tile (128 bytes of fp16)
-constexpr int kDequantGroups = 2;              // groups of four dequantiser warps, one per 64-k half of a stage
-constexpr int kWProducerWarp = 2 + 4 * kDequantGroups;     // warp 10
-constexpr int kThreads  = 32 * (kWProducerWarp + 1);       // warps 0-3, 6-9: dequantisers; 4: x TMA; 5: MMA; 10: W TMA
+// GROUPS = groups of four dequantiser warps: 2 (one per 64-k half of every stage) for the 256-token tile, 4 (two
+// pairs taking stages in turn) for the smaller tiles, whose stages are shorter than one pair's latency chain.
+// Warps 0-3, 6.. : dequantisers; 4: x TMA; 5: MMA; the last warp: W TMA.
+__host__ __device__ constexpr int w_producer_warp(int groups) { return 2 + 4 * groups; }
+__host__ __device__ constexpr int tc_threads(int groups) { return 32 * (w_producer_warp(groups) + 1); }
+#ifndef W4A16_TC_GROUPS_SMALL
+#define W4A16_TC_GROUPS_SMALL 4
+#endif
+__host__ __device__ constexpr int tc_groups(int tok) { return tok == 256 ? 2 : W4A16_TC_GROUPS_SMALL; }
 constexpr int kTmemCols = 512;
 constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;   // 0.4 s: far above any legitimate wait
 
@@ -102,7 +111,7 @@ struct TcParams {
 };
 
 template <int TOK>
-__global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p)
+__global__ void __launch_bounds__(tc_threads(tc_groups(TOK)), 1) tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p)
 {
     using Cfg = TcCfg<TOK>;
     constexpr int S = Cfg::kStages, SW = Cfg::kWStages;
@@ -192,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             }
             if (!ok) drain_copies();
         }
-    } else if (warp == kWProducerWarp) {
+    } else if (warp == w_producer_warp(tc_groups(TOK))) {
         // ------------------------------ TMA producer of the packed weights ------------------------------
         // Three lanes share the copies of a stage (an issued copy holds its thread for about a hundred cycles).  A
         // copy that completes before lane 0 has armed the barrier only drives its byte count negative for a moment;
@@ -344,7 +353,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         int st = 0, sw = 0; uint32_t phase = 0, wphase = 0, dphase = 0;
         bool ok = true;
         const int r = lane >> 2;
-        const int quarter = warp & 3, dgroup = warp < 4 ? 0 : 1;
+        constexpr int GROUPS = tc_groups(TOK);
+        const int quarter = warp & 3;
+        const int wgroup = warp < 4 ? 0 : (warp - 2) / 4;              // 0 .. GROUPS-1
+        const int dgroup = wgroup & 1;                                 // which 64-k half of a stage
+        const int turn = wgroup >> 1;                                  // GROUPS == 4: which stages (even / odd)
+        uint32_t step_mod = 0;
         uint32_t epi_phase = 0;
         // bounded rendezvous of the eight dequant/epilogue warps (split-K finalisation)
         auto epi_sync = [&]() -> bool {
@@ -362,7 +376,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             const bool has_tile = nb * 4 + quarter < n_tiles;
             int ks0, ks1;
             k_range(item, ks0, ks1);
-            for (int ks = ks0; ks < ks1; ++ks) {
+            for (int ks = ks0; ks < ks1; ++ks, step_mod ^= 1u) {
+                if (GROUPS == 4 && step_mod != (uint32_t)turn) {               // the other pair's stage
+                    if (++sw == SW) { sw = 0; wphase ^= 1u; }
+                    if (++st == S) { st = 0; phase ^= 1u; }
+                    continue;
+                }
                 ok = __all_sync(0xffffffffu, mbar_wait(wfull_bar(sw), wphase, abort_flag, kWaitBudgetNs));
                 if (!ok) break;
                 const unsigned char* wst = smem + Cfg::kWRingOff + sw * Cfg::kWStageBytes;
@@ -412,6 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
                 if (++st == S) { st = 0; phase ^= 1u; }
             }
             if (!ok) break;
+            if (wgroup >= 2) continue;                                       // only the first pair drains the accumulator
 
             // epilogue: thread = out-feature (TMEM lane), registers = tokens.  The per-element loops carry no branch
             // (measured: with the bias / ReLU / residual / ragged-tile tests inside them a tile took 15 000 cycles to
@@ -625,7 +645,7 @@ int launch_tok(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev < 64) configured[dev] = 1;
     }
-    tc_kernel<TOK><<<grid, kThreads, TcCfg<TOK>::kSmemBytes, st>>>(map, p);
+    tc_kernel<TOK><<<grid, tc_threads(tc_groups(TOK)), TcCfg<TOK>::kSmemBytes, st>>>(map, p);
     count_launch();
     e = cudaGetLastError();
     return e == cudaSuccess ? W4A16_OK : record_cuda_error(e);
